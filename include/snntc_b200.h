@@ -1,0 +1,121 @@
+/*
+ * snntc_b200 -- C ABI of the B200 (sm_100a) implementation of the four SNN-TC operators.
+ *
+ * One shared library (libsnntc_b200.so), plain pointers and sizes, no framework types. Every data
+ * pointer is a DEVICE pointer except the `params*_host` vectors, which are read on the host (the
+ * reference pins `params` to host memory as well: snntc/snnfc_kernels.cc:224). The library allocates
+ * nothing: outputs and the scratch `workspace` belong to the caller, who sizes the workspace with the
+ * matching *_workspace_bytes() call. All work is queued on `stream` (a cudaStream_t passed as void*)
+ * and the call returns without waiting for it; the reference blocks the host after every launch
+ * (snntc/snnfc_kernels.cu.cc:187), callers that relied on that must synchronise the stream.
+ *
+ * Every entry point returns 0 on success or a negative SNNTC_E_* code (see snntc_status_string);
+ * nothing is printed and nothing aborts.
+ */
+#ifndef SNNTC_B200_H_
+#define SNNTC_B200_H_
+
+#include <stddef.h>
+
+#if defined(__GNUC__)
+#define SNNTC_API __attribute__((visibility("default")))
+#else
+#define SNNTC_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SNNTC_OK = 0,
+  SNNTC_E_NULL = -1,       /* a required pointer is null */
+  SNNTC_E_SHAPE = -2,      /* a dimension is <= 0 or inconsistent (e.g. grad rows != 2*B) */
+  SNNTC_E_WEIGHT_ROWS = -3,/* weight rows != fan-in (+1 when params say bias is on) */
+  SNNTC_E_TOO_LARGE = -4,  /* a tensor has more than 2^31-1 elements */
+  SNNTC_E_WORKSPACE = -5,  /* workspace pointer null/misaligned or smaller than *_workspace_bytes() */
+  SNNTC_E_UNSUPPORTED = -6,/* configuration the kernels cannot run (e.g. fan-in too large for shared memory) */
+  SNNTC_E_CUDA = -7,       /* a CUDA runtime call failed; see snntc_last_cuda_error() */
+  SNNTC_E_PARAMS = -8      /* params vector holds an invalid kernel size / stride / sentinel */
+};
+
+SNNTC_API const char* snntc_status_string(int status);
+/* Text of the last CUDA runtime error seen by this thread inside the library ("" if none). */
+SNNTC_API const char* snntc_last_cuda_error(void);
+/* Library version, e.g. "snntc_b200 0.1 sm_100a". */
+SNNTC_API const char* snntc_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * SnnFc -- dense forward.  Replaces the op registered at snntc/snnfc_ops.cc:6-30 with the kernel
+ * dispatch of snntc/snnfc_kernels.cc:155-208 and the GPU functor snntc/snnfc_kernels.cu.cc:93-194.
+ *   x[B,I] row-major inputs (spike values z=exp(t)); w[w_rows,J] with w_rows = I (+1 bias row, LAST)
+ *   params6_host = [MAX_SPIKE_TIME, Epsilon, Spike_Threshold, Thread_per_Block, Blocks, biasvolt]
+ *                  (SNN_TC_Modules.py:48-49; entries 1,3,4 are accepted and ignored)
+ *   out[2B,J]: rows [0,B) spike value or MAX; rows [B,2B) 1/(sum w - threshold) or 0.
+ */
+SNNTC_API size_t snntc_fc_forward_workspace_bytes(int B, int I, int J);
+SNNTC_API int snntc_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
+                     int B, int I, int w_rows, int J,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * SnnFcGrad -- dense backward.  Replaces snntc/snnfcgrad_ops.cc:6-23, snntc/snnfcgrad_kernels.cc:88-132
+ * and the GPU functor snntc/snnfcgrad_kernels.cu.cc:137-225.
+ *   grad[2B,J] (only rows [0,B) are read), out[2B,J] = the forward's output.
+ *   dx[B,I] may be null (first layer of a network); dw[w_rows,J]; dparams6 (device, may be null) is
+ *   zero-filled -- the reference never writes it on the GPU.
+ */
+SNNTC_API size_t snntc_fc_backward_workspace_bytes(int B, int I, int w_rows, int J);
+SNNTC_API int snntc_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
+                      const float* out_2BJ, float* dx, float* dw, float* dparams6,
+                      int B, int I, int w_rows, int J,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * SnnCv -- convolution forward.  Replaces snntc/snncv_ops.cc:6-35, snntc/snncv_kernels.cc:186-243 and
+ * the GPU functor snntc/snncv_kernels.cu.cc:95-210 (im2col + segmented sort + walk, here fused).
+ *   x[B,H,W,C] NHWC, UNPADDED. The reference op receives a tensor already padded with MAX by
+ *   SNN_conv.call (SNN_TC_Modules.py:147-161); here pad_top/pad_left say where the image sits in that
+ *   virtual padded frame and taps outside [0,H)x[0,W) read as MAX. pad_top = pad_left = 0 with
+ *   Nh=(H-Kh)/Sh+1 reproduces the reference op on a pre-padded tensor exactly.
+ *   w[w_rows,Kc], row (kh*Kw+kw)*C+c, bias row last.
+ *   params12_host = [MAX, Thread_per_Block, Blocks, Epsilon, Threshold, cudaflag, Kh, Kw, Sh, Sw,
+ *                    SAME?1:0, biasvolt] (SNN_TC_Modules.py:121-123)
+ *   out[2B,Nh,Nw,Kc] packed like SnnFc.
+ */
+SNNTC_API size_t snntc_cv_forward_workspace_bytes(int B, int H, int W, int C, int Kc, int Kh, int Kw, int Nh, int Nw);
+SNNTC_API int snntc_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                     int B, int H, int W, int C, int w_rows, int Kc,
+                     int pad_top, int pad_left, int Nh, int Nw,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * SnnCvGrad -- convolution backward.  Replaces snntc/snncvgrad_ops.cc:6-23,
+ * snntc/snncvgrad_kernels.cc:126-184 and the GPU functor snntc/snncvgrad_kernels.cu.cc:164-263.
+ *   dx[B,H,W,C] is the gradient of the UNPADDED input (what tf.pad's gradient leaves of the
+ *   reference's padded-shape result); it is written, not accumulated, and may be null.
+ */
+SNNTC_API size_t snntc_cv_backward_workspace_bytes(int B, int H, int W, int C, int w_rows, int Kc, int Nh, int Nw);
+SNNTC_API int snntc_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
+                      const float* out, float* dx, float* dw, float* dparams12,
+                      int B, int H, int W, int C, int w_rows, int Kc,
+                      int pad_top, int pad_left, int Nh, int Nw,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Earliest-spike pooling between conv layers. The reference has no native code for it: SNN_maxpool2d
+ * pads with 1e5 and calls -MaxPool2D(-x) in TensorFlow (SNN_TC_Modules.py:216-246). Here: window
+ * minimum over the UNPADDED NHWC input with out-of-image taps reading `padvalue`; arg[B,Nh,Nw,C]
+ * receives the flat input index of each winner (first minimum in (kh,kw) order, -1 for padding) and
+ * drives the backward, which zero-fills dx[n_in] and adds gy[o] at arg[o].
+ */
+SNNTC_API int snntc_minpool_forward(const float* x_nhwc, float* y, int* arg, int B, int H, int W, int C,
+                                    int Kh, int Kw, int Sh, int Sw, int pad_top, int pad_left, int Nh, int Nw,
+                                    float padvalue, void* stream);
+SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx, size_t n_out, size_t n_in,
+                                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SNNTC_B200_H_ */

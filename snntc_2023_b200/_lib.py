@@ -1,0 +1,75 @@
+"""ctypes binding of libsnntc_b200.so (the C ABI declared in include/snntc_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsnntc_b200.so")
+
+# every symbol include/snntc_b200.h declares: (restype, argtypes)
+_F = ctypes.c_void_p  # device/host float pointers travel as integers
+_INT = ctypes.c_int
+_SZ = ctypes.c_size_t
+SYMBOLS = {
+    "snntc_status_string": (ctypes.c_char_p, [_INT]),
+    "snntc_last_cuda_error": (ctypes.c_char_p, []),
+    "snntc_version": (ctypes.c_char_p, []),
+    "snntc_fc_forward_workspace_bytes": (_SZ, [_INT] * 3),
+    "snntc_fc_forward": (_INT, [_F, _F, _F, _F] + [_INT] * 4 + [_F, _SZ, _F]),
+    "snntc_fc_backward_workspace_bytes": (_SZ, [_INT] * 4),
+    "snntc_fc_backward": (_INT, [_F] * 8 + [_INT] * 4 + [_F, _SZ, _F]),
+    "snntc_cv_forward_workspace_bytes": (_SZ, [_INT] * 9),
+    "snntc_cv_forward": (_INT, [_F] * 4 + [_INT] * 10 + [_F, _SZ, _F]),
+    "snntc_cv_backward_workspace_bytes": (_SZ, [_INT] * 8),
+    "snntc_cv_backward": (_INT, [_F] * 8 + [_INT] * 10 + [_F, _SZ, _F]),
+    "snntc_minpool_forward": (_INT, [_F, _F, _F] + [_INT] * 12 + [ctypes.c_float, _F]),
+    "snntc_minpool_backward": (_INT, [_F, _F, _F] + [_SZ, _SZ, _F]),
+    "snntc_fc_backward_noalloc": (_INT, [_F] * 8 + [_INT] * 4 + [_F]),
+    "snntc_noalloc_scratch_bytes": (_SZ, []),
+}
+OPTIONAL = {"snntc_minpool_forward", "snntc_minpool_backward", "snntc_fc_backward_noalloc",
+            "snntc_noalloc_scratch_bytes"}
+
+_lib = None
+
+
+class SnntcError(RuntimeError):
+    pass
+
+
+def load():
+    """Loads the library once; raises if it has not been built (python -m snntc_2023_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise SnntcError(
+            "libsnntc_b200.so not found at %s -- build it with `python -m snntc_2023_b200.build`; "
+            "there is no CPU or framework fallback" % LIB_PATH)
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            if name in OPTIONAL:
+                continue
+            raise SnntcError("libsnntc_b200.so does not export %s" % name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status, what):
+    """Turns a non-zero status into the exception the reference would have raised as InvalidArgument."""
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.snntc_status_string(status).decode()
+    if status == -7:
+        raise SnntcError("%s: %s (%s)" % (what, msg, lib.snntc_last_cuda_error().decode()))
+    if status in (-1, -2, -3, -4, -8):
+        raise ValueError("%s: %s" % (what, msg))
+    raise SnntcError("%s: %s" % (what, msg))

@@ -1,0 +1,214 @@
+// extern "C" boundary of libsnntc_b200.so: argument validation (what the reference does in
+// OpKernel::Compute, e.g. snntc/snnfc_kernels.cc:160-207 and snntc/snncv_kernels.cc:191-242),
+// translation of the `params` vectors into a Geometry, and dispatch to the kernel launchers.
+#include "../../include/snntc_b200.h"
+#include "snntc_common.cuh"
+
+#include <limits.h>
+#include <string.h>
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+
+void note_cuda_error(cudaError_t e) {
+  if (e == cudaSuccess) return;
+  strncpy(g_cuda_err, cudaGetErrorString(e), sizeof(g_cuda_err) - 1);
+  g_cuda_err[sizeof(g_cuda_err) - 1] = 0;
+}
+
+struct DevCache { int ready; snntc::LaunchInfo li; };
+DevCache g_dev[64];
+
+int launch_info(snntc::LaunchInfo* li) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
+  if (dev >= 0 && dev < 64 && g_dev[dev].ready) { *li = g_dev[dev].li; return SNNTC_OK; }
+  int sms = 0, smem = 0;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+  if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
+  li->num_sms = sms;
+  li->max_smem_optin = smem;
+  if (dev >= 0 && dev < 64) { g_dev[dev].li = *li; g_dev[dev].ready = 1; }
+  return SNNTC_OK;
+}
+
+// Launch planning that must also work where no device is visible (workspace queries on a build host):
+// fall back to the B200 figures.
+snntc::LaunchInfo launch_info_or_default() {
+  snntc::LaunchInfo li;
+  if (launch_info(&li) != SNNTC_OK) { li.num_sms = 148; li.max_smem_optin = 232448; cudaGetLastError(); }
+  return li;
+}
+
+bool fits_int32(long long n) { return n >= 0 && n <= (long long)INT_MAX; }
+
+int fc_geometry(const float* p, int B, int I, int w_rows, int J, snntc::Geometry* g) {
+  if (!p) return SNNTC_E_NULL;
+  if (B <= 0 || I <= 0 || J <= 0 || w_rows <= 0) return SNNTC_E_SHAPE;
+  memset(g, 0, sizeof(*g));
+  g->is_conv = 0;
+  g->R = B; g->I = I; g->J = J;
+  g->maxv = p[0]; g->theta = p[2]; g->biasvolt = p[5];
+  g->has_bias = g->biasvolt > 1e-8f ? 1 : 0;
+  if (!(g->maxv > 1.0f)) return SNNTC_E_PARAMS;
+  if (w_rows != I + g->has_bias) return SNNTC_E_WEIGHT_ROWS;
+  if (!fits_int32((long long)B * I) || !fits_int32((long long)w_rows * J) || !fits_int32(2LL * B * J))
+    return SNNTC_E_TOO_LARGE;
+  return SNNTC_OK;
+}
+
+int cv_geometry(const float* p, int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left,
+                int Nh, int Nw, snntc::Geometry* g) {
+  if (!p) return SNNTC_E_NULL;
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || Kc <= 0 || w_rows <= 0 || Nh <= 0 || Nw <= 0 || pad_top < 0 || pad_left < 0)
+    return SNNTC_E_SHAPE;
+  memset(g, 0, sizeof(*g));
+  g->is_conv = 1;
+  g->maxv = p[0]; g->theta = p[4]; g->biasvolt = p[11];
+  g->has_bias = g->biasvolt > 1e-8f ? 1 : 0;
+  g->Kh = (int)p[6]; g->Kw = (int)p[7]; g->Sh = (int)p[8]; g->Sw = (int)p[9];
+  if (!(g->maxv > 1.0f) || g->Kh <= 0 || g->Kw <= 0 || g->Sh <= 0 || g->Sw <= 0) return SNNTC_E_PARAMS;
+  g->B = B; g->H = H; g->W = W; g->C = C; g->Nh = Nh; g->Nw = Nw; g->pad_top = pad_top; g->pad_left = pad_left;
+  if (pad_top >= g->Kh || pad_left >= g->Kw) return SNNTC_E_SHAPE;   // a whole tap row/column of padding is never produced
+  const long long I = (long long)g->Kh * g->Kw * C;
+  const long long R = (long long)B * Nh * Nw;
+  if (!fits_int32(I) || !fits_int32(R)) return SNNTC_E_TOO_LARGE;
+  g->I = (int)I; g->R = (int)R; g->J = Kc;
+  if (w_rows != g->I + g->has_bias) return SNNTC_E_WEIGHT_ROWS;
+  // same limits as the reference: input, weight, packed output and the (virtual) patch matrix
+  if (!fits_int32((long long)B * H * W * C) || !fits_int32((long long)w_rows * Kc) || !fits_int32(2LL * R * Kc) ||
+      !fits_int32(R * (long long)w_rows))
+    return SNNTC_E_TOO_LARGE;
+  return SNNTC_OK;
+}
+
+int check_ws(void* ws, size_t have, size_t need) {
+  if (need == 0) return SNNTC_OK;
+  if (!ws || have < need || ((uintptr_t)ws & 15)) return SNNTC_E_WORKSPACE;
+  return SNNTC_OK;
+}
+
+int finish(int rc) {
+  if (rc == snntc::E_CUDA) note_cuda_error(cudaGetLastError());
+  return rc;
+}
+
+int run_forward(const snntc::Geometry& g, const float* x, const float* w, float* out, void* ws, size_t wsb, void* stream) {
+  snntc::LaunchInfo li;
+  int rc = launch_info(&li);
+  if (rc) return rc;
+  rc = check_ws(ws, wsb, snntc::forward_workspace_bytes(g));
+  if (rc) return rc;
+  return finish(snntc::launch_forward(g, x, w, out, ws, wsb, li, (cudaStream_t)stream));
+}
+
+int run_backward(const snntc::Geometry& g, const float* grad, const float* x, const float* w, const float* out,
+                 float* dx, float* dw, float* dparams, int nparams, void* ws, size_t wsb, void* stream) {
+  snntc::LaunchInfo li;
+  int rc = launch_info(&li);
+  if (rc) return rc;
+  rc = check_ws(ws, wsb, snntc::backward_workspace_bytes(g, li));
+  if (rc) return rc;
+  if (dparams) {
+    cudaError_t e = cudaMemsetAsync(dparams, 0, sizeof(float) * nparams, (cudaStream_t)stream);
+    if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
+  }
+  return finish(snntc::launch_backward(g, grad, x, w, out, dx, dw, ws, wsb, li, (cudaStream_t)stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* snntc_status_string(int status) {
+  switch (status) {
+    case SNNTC_OK: return "ok";
+    case SNNTC_E_NULL: return "null pointer argument";
+    case SNNTC_E_SHAPE: return "invalid or inconsistent dimensions";
+    case SNNTC_E_WEIGHT_ROWS: return "input and weight inner dimensions mismatch (weight rows must be fan-in, +1 with bias)";
+    case SNNTC_E_TOO_LARGE: return "too many elements in a tensor (limit 2^31-1)";
+    case SNNTC_E_WORKSPACE: return "workspace missing, misaligned or too small";
+    case SNNTC_E_UNSUPPORTED: return "configuration not supported by the sm_100a kernels";
+    case SNNTC_E_CUDA: return "CUDA runtime error";
+    case SNNTC_E_PARAMS: return "invalid params vector";
+    default: return "unknown status";
+  }
+}
+
+const char* snntc_last_cuda_error(void) { return g_cuda_err; }
+
+const char* snntc_version(void) { return "snntc_b200 0.1 sm_100a"; }
+
+size_t snntc_fc_forward_workspace_bytes(int B, int I, int J) {
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.R = B; g.I = I; g.J = J;
+  return snntc::forward_workspace_bytes(g);
+}
+
+int snntc_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
+                     int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w || !out_2BJ) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
+  if (rc) return rc;
+  return run_forward(g, x, w, out_2BJ, workspace, workspace_bytes, stream);
+}
+
+size_t snntc_fc_backward_workspace_bytes(int B, int I, int w_rows, int J) {
+  if (B <= 0 || I <= 0 || J <= 0 || w_rows < I) return 0;
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.R = B; g.I = I; g.J = J; g.has_bias = w_rows > I ? 1 : 0;
+  return snntc::backward_workspace_bytes(g, launch_info_or_default());
+}
+
+int snntc_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
+                      const float* out_2BJ, float* dx, float* dw, float* dparams6,
+                      int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grad_2BJ || !x || !w || !out_2BJ || !dw) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
+  if (rc) return rc;
+  return run_backward(g, grad_2BJ, x, w, out_2BJ, dx, dw, dparams6, 6, workspace, workspace_bytes, stream);
+}
+
+size_t snntc_cv_forward_workspace_bytes(int B, int H, int W, int C, int Kc, int Kh, int Kw, int Nh, int Nw) {
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.is_conv = 1; g.B = B; g.H = H; g.W = W; g.C = C; g.J = Kc; g.Kh = Kh; g.Kw = Kw; g.Nh = Nh; g.Nw = Nw;
+  g.I = Kh * Kw * C; g.R = B * Nh * Nw;
+  return snntc::forward_workspace_bytes(g);
+}
+
+int snntc_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                     int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x_nhwc || !w || !out) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
+  if (rc) return rc;
+  return run_forward(g, x_nhwc, w, out, workspace, workspace_bytes, stream);
+}
+
+size_t snntc_cv_backward_workspace_bytes(int B, int H, int W, int C, int w_rows, int Kc, int Nh, int Nw) {
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || Kc <= 0 || w_rows <= 0 || Nh <= 0 || Nw <= 0) return 0;
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.is_conv = 1; g.B = B; g.H = H; g.W = W; g.C = C; g.J = Kc; g.Nh = Nh; g.Nw = Nw;
+  g.I = w_rows; g.has_bias = 0;   // planning depends only on the total weight rows
+  g.R = B * Nh * Nw;
+  return snntc::backward_workspace_bytes(g, launch_info_or_default());
+}
+
+int snntc_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
+                      const float* out, float* dx, float* dw, float* dparams12,
+                      int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  if (!grad || !x_nhwc || !w || !out || !dw) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
+  if (rc) return rc;
+  return run_backward(g, grad, x_nhwc, w, out, dx, dw, dparams12, 12, workspace, workspace_bytes, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,319 @@
+// SNN-TC backward (SnnFcGrad / SnnCvGrad) for sm_100a: threshold-masked reductions on FP32 CUDA cores.
+//
+//   u[r,j]  = y[r,j] fired ? grad[r,j] * inv[r,j] : 0                       (snnfcgrad_kernels.cu.cc:171-172)
+//   dX[r,i] = sum_j [x_ri <= y_rj] u_rj W[i,j]                              (snnfcgrad_kernels.cu.cc:56-65)
+//   dW[i,j] = sum_r [x_ri <= y_rj] (x_ri - y_rj) u_rj, bias row uses x=biasvolt (snnfcgrad_kernels.cu.cc:100-120)
+//
+// Both are register-tiled like an SGEMM (64x64 CTA tile, 4x4 per thread) with the predicate applied
+// per element. The same two kernels serve the convolution: dX is tiled by INPUT pixel and loops over
+// the Kh*Kw taps, gathering the covering receptive fields, so no atomics are needed (the reference
+// scatters with atomicAdd, snncvgrad_kernels.cu.cc:83); dW gathers its x tile straight from the
+// NHWC image. dW splits the row dimension over CTAs and a second kernel adds the partial tiles in a
+// fixed order, so results are reproducible run to run.
+#include "snntc_common.cuh"
+
+#include <math_constants.h>
+
+namespace snntc {
+
+namespace {
+
+constexpr int kBwdThreads = 256;
+constexpr int kTile = 64;       // CTA tile edge (rows x columns of the output)
+constexpr int kJT = 16;         // reduction chunk of the dX kernel (outputs j per shared-memory tile)
+constexpr int kJTP = kJT + 4;   // padded row stride: keeps float4 alignment, spreads rows over banks
+constexpr int kRT = 16;         // reduction chunk of the dW kernel (rows r per shared-memory tile)
+
+// ------------------------------------------------------------------------------------------- dX
+// "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C).
+__global__ void __launch_bounds__(kBwdThreads)
+snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
+              const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
+  __shared__ __align__(16) float Ys[kTile * kJTP];
+  __shared__ __align__(16) float Us[kTile * kJTP];
+  __shared__ __align__(16) float Ws[kTile * kJTP];
+  __shared__ int s_orow[kTile];
+
+  const int J = g.J;
+  const int CH = g.is_conv ? g.C : g.I;
+  const int P = g.is_conv ? g.B * g.H * g.W : g.R;
+  const int taps = g.is_conv ? g.Kh * g.Kw : 1;
+  const float maxcomp = g.maxv - 0.1f;
+  const float* __restrict__ yv = out;
+  const float* __restrict__ iv = out + (size_t)g.R * J;
+
+  const int tid = threadIdx.x;
+  const int tr = tid >> 4, ti = tid & 15;
+  const int p0 = blockIdx.x * kTile, c0 = blockIdx.y * kTile;
+
+  float xr[4][4], acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int p = p0 + tr + 16 * a, c = c0 + ti + 16 * b;
+      xr[a][b] = (p < P && c < CH) ? __ldg(x + (size_t)p * CH + c) : CUDART_INF_F;
+      acc[a][b] = 0.f;
+    }
+
+  const int ld_jj = tid & 15, ld_row = tid >> 4;  // tile loaders: 16 consecutive j per row
+
+  for (int tap = 0; tap < taps; ++tap) {
+    // which output row (receptive field) does each point of the tile feed through this tap?
+    if (tid < kTile) {
+      const int p = p0 + tid;
+      int orow = -1;
+      if (p < P) {
+        if (!g.is_conv) {
+          orow = p;
+        } else {
+          const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
+          const int ww = p % g.W;
+          const int t = p / g.W;
+          const int h = t % g.H;
+          const int b = t / g.H;
+          const int hh = h + g.pad_top - kh, wq = ww + g.pad_left - kw;
+          if (hh >= 0 && wq >= 0 && hh % g.Sh == 0 && wq % g.Sw == 0) {
+            const int nh = hh / g.Sh, nw = wq / g.Sw;
+            if (nh < g.Nh && nw < g.Nw) orow = (b * g.Nh + nh) * g.Nw + nw;
+          }
+        }
+      }
+      s_orow[tid] = orow;
+    }
+    __syncthreads();
+
+    for (int j0 = 0; j0 < J; j0 += kJT) {
+      const int j = j0 + ld_jj;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int row = ld_row + 16 * q;
+        const int orow = s_orow[row];
+        float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
+        if (orow >= 0 && j < J) {
+          const size_t o = (size_t)orow * J + j;
+          y = __ldg(yv + o);
+          u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
+        }
+        const int c = c0 + row;
+        if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
+        Ys[row * kJTP + ld_jj] = y;
+        Us[row * kJTP + ld_jj] = u;
+        Ws[row * kJTP + ld_jj] = wv;
+      }
+      __syncthreads();
+
+#pragma unroll
+      for (int j4 = 0; j4 < kJT; j4 += 4) {
+        float4 y4[4], u4[4], w4[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          y4[a] = *reinterpret_cast<const float4*>(&Ys[(tr + 16 * a) * kJTP + j4]);
+          u4[a] = *reinterpret_cast<const float4*>(&Us[(tr + 16 * a) * kJTP + j4]);
+        }
+#pragma unroll
+        for (int b = 0; b < 4; ++b) w4[b] = *reinterpret_cast<const float4*>(&Ws[(ti + 16 * b) * kJTP + j4]);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            const float xv = xr[a][b];
+            if (xv <= y4[a].x) acc[a][b] = fmaf(u4[a].x, w4[b].x, acc[a][b]);
+            if (xv <= y4[a].y) acc[a][b] = fmaf(u4[a].y, w4[b].y, acc[a][b]);
+            if (xv <= y4[a].z) acc[a][b] = fmaf(u4[a].z, w4[b].z, acc[a][b]);
+            if (xv <= y4[a].w) acc[a][b] = fmaf(u4[a].w, w4[b].w, acc[a][b]);
+          }
+      }
+      __syncthreads();
+    }
+  }
+
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int p = p0 + tr + 16 * a, c = c0 + ti + 16 * b;
+      if (p < P && c < CH) dx[(size_t)p * CH + c] = acc[a][b];
+    }
+}
+
+// ------------------------------------------------------------------------------------------- dW
+// Output tile 64 (fan-in rows i, bias row included) x 64 (outputs j); blockIdx.z selects a slice of
+// the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane of the workspace.
+__global__ void __launch_bounds__(kBwdThreads)
+snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
+              const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
+  __shared__ __align__(16) float Xs[kRT * kTile];
+  __shared__ __align__(16) float Ys[kRT * kTile];
+  __shared__ __align__(16) float Us[kRT * kTile];
+  __shared__ int s_b[kRT], s_h0[kRT], s_w0[kRT];
+
+  const int J = g.J, I = g.I, R = g.R;
+  const int Itot = I + g.has_bias;
+  const float maxcomp = g.maxv - 0.1f;
+  const float* __restrict__ yv = out;
+  const float* __restrict__ iv = out + (size_t)R * J;
+
+  const int tid = threadIdx.x;
+  const int ti = tid >> 4, tj = tid & 15;
+  const int i0 = blockIdx.y * kTile, j0 = blockIdx.x * kTile;
+  const int r_begin = blockIdx.z * rows_per_split;
+  const int r_end = min(R, r_begin + rows_per_split);
+
+  // loader role: one fixed column of the tile, rows ld_r, ld_r+4, ...
+  const int ld_c = tid & 63, ld_r = tid >> 6;
+  const int li = i0 + ld_c;   // fan-in index this thread loads
+  const int lj = j0 + ld_c;   // output index this thread loads
+  int l_kh = 0, l_kw = 0, l_c = 0;
+  if (g.is_conv && li < I) {
+    const int tap = li / g.C;
+    l_c = li - tap * g.C;
+    l_kh = tap / g.Kw;
+    l_kw = tap - l_kh * g.Kw;
+  }
+
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+
+  for (int rb = r_begin; rb < r_end; rb += kRT) {
+    if (g.is_conv && tid < kRT) {
+      const int r = rb + tid;
+      if (r < r_end) {
+        const int nw = r % g.Nw;
+        const int t = r / g.Nw;
+        const int nh = t % g.Nh;
+        s_b[tid] = t / g.Nh;
+        s_h0[tid] = nh * g.Sh - g.pad_top;
+        s_w0[tid] = nw * g.Sw - g.pad_left;
+      }
+    }
+    if (g.is_conv) __syncthreads();
+
+#pragma unroll
+    for (int q = 0; q < kRT / 4; ++q) {
+      const int rr = ld_r + 4 * q;
+      const int r = rb + rr;
+      float xv = CUDART_INF_F, y = -CUDART_INF_F, u = 0.f;
+      if (r < r_end) {
+        if (li < I) {
+          if (!g.is_conv) {
+            xv = __ldg(x + (size_t)r * I + li);
+          } else {
+            const int h = s_h0[rr] + l_kh, ww = s_w0[rr] + l_kw;
+            if (h >= 0 && h < g.H && ww >= 0 && ww < g.W)
+              xv = __ldg(x + (((size_t)s_b[rr] * g.H + h) * g.W + ww) * g.C + l_c);
+          }
+        } else if (li == I && g.has_bias) {
+          xv = g.biasvolt;
+        }
+        if (lj < J) {
+          const size_t o = (size_t)r * J + lj;
+          y = __ldg(yv + o);
+          u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
+        }
+      }
+      Xs[rr * kTile + ld_c] = xv;
+      Ys[rr * kTile + ld_c] = y;
+      Us[rr * kTile + ld_c] = u;
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int rr = 0; rr < kRT; ++rr) {
+      const float4 x4 = *reinterpret_cast<const float4*>(&Xs[rr * kTile + 4 * ti]);
+      const float4 y4 = *reinterpret_cast<const float4*>(&Ys[rr * kTile + 4 * tj]);
+      const float4 u4 = *reinterpret_cast<const float4*>(&Us[rr * kTile + 4 * tj]);
+      const float xa[4] = {x4.x, x4.y, x4.z, x4.w};
+      const float ya[4] = {y4.x, y4.y, y4.z, y4.w};
+      const float ua[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          // [x<=y]*(x-y) == min(x,y)-y, bit for bit, and is 0 for sentinel inputs (x > every fired y)
+          const float d = fminf(xa[a], ya[b]) - ya[b];
+          acc[a][b] = fmaf(d, ua[b], acc[a][b]);
+        }
+    }
+    __syncthreads();
+  }
+
+  float* __restrict__ dst = partial + (size_t)blockIdx.z * Itot * J;
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int i = i0 + 4 * ti + a, j = j0 + 4 * tj + b;
+      if (i < Itot && j < J) dst[(size_t)i * J + j] = acc[a][b];
+    }
+}
+
+__global__ void snn_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, size_t n, int splits) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + e];
+    dw[e] = s;
+  }
+}
+
+struct DwPlan { int splits; int rows_per_split; };
+
+DwPlan plan_dw(const Geometry& g, const LaunchInfo& li) {
+  const int Itot = g.I + g.has_bias;
+  const long tiles = (long)((Itot + kTile - 1) / kTile) * ((g.J + kTile - 1) / kTile);
+  long want = (3L * li.num_sms + tiles - 1) / tiles;
+  long max_splits = ((long)g.R + 4 * kRT - 1) / (4 * kRT);
+  if (want > max_splits) want = max_splits;
+  if (want > 256) want = 256;
+  if (want < 1) want = 1;
+  long rps = ((long)g.R + want - 1) / want;
+  rps = (rps + kRT - 1) / kRT * kRT;
+  DwPlan p;
+  p.rows_per_split = (int)rps;
+  p.splits = (int)(((long)g.R + rps - 1) / rps);
+  return p;
+}
+
+}  // namespace
+
+size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
+  const DwPlan p = plan_dw(g, li);
+  if (p.splits <= 1) return 0;
+  return (size_t)p.splits * (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
+}
+
+int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
+                    float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, cudaStream_t s) {
+  const int Itot = g.I + g.has_bias;
+  if (dx) {
+    const int CH = g.is_conv ? g.C : g.I;
+    const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
+    dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
+    snn_dx_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, w, out, dx);
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  }
+  const DwPlan p = plan_dw(g, li);
+  float* partial = dw;
+  if (p.splits > 1) {
+    const size_t need = (size_t)p.splits * Itot * g.J * sizeof(float);
+    if (!ws || ws_bytes < need) return -5;
+    partial = static_cast<float*>(ws);
+  }
+  dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTile - 1) / kTile, p.splits);
+  snn_dw_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, out, partial, p.rows_per_split);
+  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  if (p.splits > 1) {
+    const size_t n = (size_t)Itot * g.J;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
+    snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, p.splits);
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  }
+  return OK;
+}
+
+}  // namespace snntc

@@ -1,0 +1,97 @@
+"""GPU parity of SnnFc / SnnFcGrad against the oracle, through the C ABI (ctypes) on torch buffers."""
+import numpy as np
+import pytest
+
+import oracle as O
+from tests import parity as P
+
+pytestmark = pytest.mark.gpu
+
+# (seed, B, I, J, biasvolt, dist) -- shapes in the spirit of test-snn-fc-forward.py:25-32 (1..1000, odd sizes)
+DENSE_CASES = [
+    (11, 37, 300, 200, 1.0, "test"),
+    (12, 64, 784, 400, 0.0, "cfg"),
+    (13, 5, 1, 1, 1.0, "test"),
+    (14, 1, 17, 33, 0.0, "test"),
+    (15, 129, 999, 65, 1.0, "test"),
+    (16, 70, 513, 10, 1.0, "cfg"),
+    (17, 33, 64, 130, 0.5, "test"),
+    (18, 16, 2049, 96, 1.0, "cfg"),
+]
+
+
+def _run_dense(seed, B, I, J, bv, dist):
+    import torch
+    from snntc_2023_b200 import ops
+    x, w = P.make_inputs(seed, (B, I), (I + (bv > 1e-8), J), dist)
+    params = O.fc_params(biasvolt=bv)
+    dev = torch.device("cuda:0")
+    xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
+    out = ops.snn_fc(xd, wd, params)
+    assert out.shape == (2 * B, J)
+    outc = out.cpu().numpy()
+    return x, w, params, xd, wd, out, outc
+
+
+@pytest.mark.parametrize("case", DENSE_CASES, ids=lambda c: "s%d_B%d_I%d_J%d_b%g_%s" % c)
+def test_dense_forward(case):
+    seed, B, I, J, bv, dist = case
+    x, w, params, xd, wd, out, outc = _run_dense(*case)
+    o32 = O.fc_forward(x, w, params, "f32")
+    o64 = O.fc_forward(x, w, params, "f64")
+    P.check_forward(outc[:B], outc[B:], o32, o64, rows=x, what="dense fwd %s" % (case,))
+
+
+@pytest.mark.parametrize("case", DENSE_CASES, ids=lambda c: "s%d_B%d_I%d_J%d_b%g_%s" % c)
+def test_dense_backward(case):
+    import torch
+    from snntc_2023_b200 import ops
+    seed, B, I, J, bv, dist = case
+    x, w, params, xd, wd, out, outc = _run_dense(*case)
+    rng = np.random.default_rng(seed + 1000)
+    g = rng.standard_normal((B, J)).astype(np.float32)
+    g2 = np.concatenate([g, np.zeros_like(g)])
+    dx, dw, dp = ops.snn_fc_grad(torch.from_numpy(g2).cuda(), xd, wd, params, out)
+    ref = O.fc_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    P.check_close(dx.cpu().numpy(), ref["dx"], "dense dX %s" % (case,))
+    P.check_close(dw.cpu().numpy(), ref["dw"], "dense dW %s" % (case,))
+    assert np.all(dp.cpu().numpy() == 0)
+    # the unpacked [B,J] gradient gives the same result, and dx may be skipped
+    dx2, dw2, _ = ops.snn_fc_grad(torch.from_numpy(g).cuda(), xd, wd, params, out, need_input_grad=False)
+    assert dx2 is None
+    assert torch.equal(dw2, dw)
+
+
+def test_dense_sentinel_inputs():
+    """Inputs at MAX never spike and get no gradient (snnfc_kernels.cu.cc:45, snnfcgrad_kernels.cu.cc:113)."""
+    import torch
+    from snntc_2023_b200 import ops
+    seed, B, I, J, bv = 21, 9, 40, 50, 1.0
+    x, w = P.make_inputs(seed, (B, I), (I + 1, J), "test")
+    x[:, ::3] = 1e5
+    x[0, :] = 1e5
+    params = O.fc_params(biasvolt=bv)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    out = ops.snn_fc(xd, wd, params)
+    outc = out.cpu().numpy()
+    P.check_forward(outc[:B], outc[B:], O.fc_forward(x, w, params, "f32"), O.fc_forward(x, w, params, "f64"),
+                    what="sentinel fwd")
+    g = np.random.default_rng(3).standard_normal((B, J)).astype(np.float32)
+    dx, dw, _ = ops.snn_fc_grad(torch.from_numpy(g).cuda(), xd, wd, params, out)
+    ref = O.fc_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    P.check_close(dx.cpu().numpy(), ref["dx"], "sentinel dX")
+    P.check_close(dw.cpu().numpy(), ref["dw"], "sentinel dW")
+    assert np.all(dx.cpu().numpy()[:, ::3] == 0)
+
+
+def test_dense_repeatable():
+    """No atomics on the dense path: two runs give identical bits."""
+    import torch
+    from snntc_2023_b200 import ops
+    x, w, params, xd, wd, out, outc = _run_dense(31, 100, 300, 77, 1.0, "test")
+    out2 = ops.snn_fc(xd, wd, params)
+    assert torch.equal(out, out2)
+    g = torch.randn(100, 77, device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    a = ops.snn_fc_grad(g, xd, wd, params, out)
+    b = ops.snn_fc_grad(g, xd, wd, params, out)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
