@@ -109,15 +109,16 @@ def fc_forward(x, w, params6, acc="f32", tol=1e-5):
         y = np.zeros((B, J), np.float32); inv = np.zeros((B, J), np.float32)
         rc = lib().oracle_rows_forward_f32(_p(x, _F), _p(w, _F), B, I, J, ctypes.c_float(maxv), ctypes.c_float(theta),
                                            ctypes.c_float(bv), _p(y, _F), _p(inv, _F), _p(k, _I), None,
-                                           ctypes.c_double(tol))
+                                           ctypes.c_double(tol), None)
         assert rc == 0
         return dict(y=y, inv=inv, k=k)
     y = np.zeros((B, J), np.float64); inv = np.zeros((B, J), np.float64); ill = np.zeros((B, J), np.uint8)
+    cond = np.zeros((B, J), np.float64)
     rc = lib().oracle_rows_forward_f64(_p(x, _F), _p(w, _F), B, I, J, ctypes.c_float(maxv), ctypes.c_float(theta),
                                        ctypes.c_float(bv), _p(y, _D), _p(inv, _D), _p(k, _I), _p(ill, _U8),
-                                       ctypes.c_double(tol))
+                                       ctypes.c_double(tol), _p(cond, _D))
     assert rc == 0
-    return dict(y=y, inv=inv, k=k, illc=ill.astype(bool))
+    return dict(y=y, inv=inv, k=k, illc=ill.astype(bool), cond=cond)
 
 
 def fc_backward(g, x, w, params6, y, inv, acc="f64", want_dx=True):
@@ -130,10 +131,12 @@ def fc_backward(g, x, w, params6, y, inv, acc="f64", want_dx=True):
                  (np.float64, _D, lib().oracle_rows_backward_f64)
     dx = np.zeros((B, I), dt) if want_dx else None
     dw = np.zeros(w.shape, dt)
+    dxa = np.zeros((B, I), np.float64) if want_dx else None
+    dwa = np.zeros(w.shape, np.float64)
     rc = fn(_p(g, _F), _p(x, _F), _p(w, _F), _p(y, _F), _p(inv, _F), B, I, J, ctypes.c_float(maxv),
-            ctypes.c_float(bv), _p(dx, pt), _p(dw, pt))
+            ctypes.c_float(bv), _p(dx, pt), _p(dw, pt), _p(dxa, _D), _p(dwa, _D))
     assert rc == 0
-    return dict(dx=dx, dw=dw)
+    return dict(dx=dx, dw=dw, dx_abs=dxa, dw_abs=dwa)
 
 
 def cv_forward(x, w, params12, acc="f32", tol=1e-5):
@@ -152,13 +155,15 @@ def cv_forward(x, w, params12, acc="f32", tol=1e-5):
             ctypes.c_float(theta), ctypes.c_float(bv))
     if acc == "f32":
         y = np.zeros(shp, np.float32); inv = np.zeros(shp, np.float32)
-        rc = lib().oracle_cv_forward_f32(*args, _p(y, _F), _p(inv, _F), _p(k, _I), None, ctypes.c_double(tol))
+        rc = lib().oracle_cv_forward_f32(*args, _p(y, _F), _p(inv, _F), _p(k, _I), None, ctypes.c_double(tol), None)
         assert rc == 0
         return dict(y=y, inv=inv, k=k)
     y = np.zeros(shp, np.float64); inv = np.zeros(shp, np.float64); ill = np.zeros(shp, np.uint8)
-    rc = lib().oracle_cv_forward_f64(*args, _p(y, _D), _p(inv, _D), _p(k, _I), _p(ill, _U8), ctypes.c_double(tol))
+    cond = np.zeros(shp, np.float64)
+    rc = lib().oracle_cv_forward_f64(*args, _p(y, _D), _p(inv, _D), _p(k, _I), _p(ill, _U8), ctypes.c_double(tol),
+                                     _p(cond, _D))
     assert rc == 0
-    return dict(y=y, inv=inv, k=k, illc=ill.astype(bool))
+    return dict(y=y, inv=inv, k=k, illc=ill.astype(bool), cond=cond)
 
 
 def cv_backward(g, x, w, params12, y, inv, acc="f64", want_dx=True):
@@ -173,10 +178,12 @@ def cv_backward(g, x, w, params12, y, inv, acc="f64", want_dx=True):
                   (np.float64, _D, lib().oracle_cv_backward_f64)
     dx = np.zeros(x.shape, dt) if want_dx else None
     dw = np.zeros(w.shape, dt)
+    dxa = np.zeros(x.shape, np.float64) if want_dx else None
+    dwa = np.zeros(w.shape, np.float64)
     rc = fn(_p(g, _F), _p(x, _F), _p(w, _F), _p(y, _F), _p(inv, _F), B, H, W, C, Kc, Kh, Kw, Sh, Sw, pt, pl,
-            Nh, Nw, ctypes.c_float(maxv), ctypes.c_float(bv), _p(dx, ptr), _p(dw, ptr))
+            Nh, Nw, ctypes.c_float(maxv), ctypes.c_float(bv), _p(dx, ptr), _p(dw, ptr), _p(dxa, _D), _p(dwa, _D))
     assert rc == 0
-    return dict(dx=dx, dw=dw)
+    return dict(dx=dx, dw=dw, dx_abs=dxa, dw_abs=dwa)
 
 
 def minpool(x, Kh, Kw, Sh, Sw, padding="SAME", padvalue=1e5):

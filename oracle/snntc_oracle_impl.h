@@ -53,11 +53,13 @@ static inline int FN(near_tie)(double ysum, double wsum, double c, double asum, 
  * y,inv   : outputs (spike value or MAX; 1/(sum w - theta) or 0)
  * kcount  : optional, number of inputs consumed before the exit
  * illc    : optional (double build only), 1 where a decision on the path to the exit
- *           was closer than `tol` (relative to x*(theta+sum|w|)) to flipping
+ *           was closer than `tol` to flipping (see near_tie)
+ * cond    : optional, (theta+sum|w|)/|sum w - theta| of a fired output: how much fp32 rounding of the
+ *           sums is amplified in y; 0 where the output did not fire
  */
 static void FN(row_forward)(const float* xs, const int* ord, int I, const float* w, int J,
                             float maxv, float theta, float biasvolt,
-                            ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol) {
+                            ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol, double* cond) {
   const ACC maxcomp = (ACC)maxv - (ACC)0.1f;
   for (int j = 0; j < J; ++j) {
     ACC wsum = -(ACC)theta, ysum = 0;
@@ -94,6 +96,7 @@ static void FN(row_forward)(const float* xs, const int* ord, int I, const float*
     inv[j] = io;
     if (kcount) kcount[j] = k;
     if (illc) illc[j] = (unsigned char)bad;
+    if (cond) cond[j] = (armed && io != 0) ? asum / fabs((double)wsum) : 0.0;
   }
 }
 
@@ -117,14 +120,15 @@ static void FN(sort_row)(const float* x, int I, float* xs, int* ord, float* tx, 
 /* Forward over R rows given as a dense matrix rows[R,I]; out is [2R,J]-packed like the op. */
 int FN(oracle_rows_forward)(const float* rows, const float* w, int R, int I, int J,
                             float maxv, float theta, float biasvolt,
-                            ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol) {
+                            ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol, double* cond) {
   float* xs = (float*)malloc(sizeof(float) * (size_t)(I > 0 ? I : 1) * 2);
   int* ord = (int*)malloc(sizeof(int) * (size_t)(I > 0 ? I : 1) * 2);
   if (!xs || !ord) { free(xs); free(ord); return -1; }
   for (int r = 0; r < R; ++r) {
     FN(sort_row)(rows + (size_t)r * I, I, xs, ord, xs + I, ord + I);
     FN(row_forward)(xs, ord, I, w, J, maxv, theta, biasvolt, y + (size_t)r * J, inv + (size_t)r * J,
-                    kcount ? kcount + (size_t)r * J : 0, illc ? illc + (size_t)r * J : 0, tol);
+                    kcount ? kcount + (size_t)r * J : 0, illc ? illc + (size_t)r * J : 0, tol,
+                    cond ? cond + (size_t)r * J : 0);
   }
   free(xs); free(ord);
   return 0;
@@ -134,10 +138,12 @@ int FN(oracle_rows_forward)(const float* rows, const float* w, int R, int I, int
  * Dense-row backward (snnfcgrad_kernels.cu.cc:56-65 for dX, :100-120 for dW).
  * g[R,J] upstream gradient of y, yv[R,J] forward spike values, iv[R,J] forward 1/(sum w - theta).
  * dx[R,I] (nullable), dw[(I+bias),J] accumulated in ACC; dw must be zeroed by the caller.
+ * dx_abs / dw_abs (nullable, zeroed by the caller) receive the sum of |terms| of every element: the
+ * scale against which fp32 summation error has to be judged.
  */
 int FN(oracle_rows_backward)(const float* g, const float* rows, const float* w, const float* yv,
                              const float* iv, int R, int I, int J, float maxv, float biasvolt,
-                             ACC* dx, ACC* dw) {
+                             ACC* dx, ACC* dw, double* dx_abs, double* dw_abs) {
   const float maxcomp = maxv - 0.1f;
   const int bias = biasvolt > 1e-8f;
   for (int r = 0; r < R; ++r) {
@@ -150,11 +156,15 @@ int FN(oracle_rows_backward)(const float* g, const float* rows, const float* w, 
         float x = xr[i];
         if (x > yj) continue;
         if (dx) dx[(size_t)r * I + i] = FMA_ACC(u, (ACC)w[(size_t)i * J + j], dx[(size_t)r * I + i]);
+        if (dx_abs) dx_abs[(size_t)r * I + i] += fabs((double)u * (double)w[(size_t)i * J + j]);
         if (x > maxcomp) continue;
         dw[(size_t)i * J + j] = FMA_ACC((ACC)x - (ACC)yj, u, dw[(size_t)i * J + j]);
+        if (dw_abs) dw_abs[(size_t)i * J + j] += fabs(((double)x - (double)yj) * (double)u);
       }
-      if (bias && !(biasvolt > yj))
+      if (bias && !(biasvolt > yj)) {
         dw[(size_t)I * J + j] = FMA_ACC((ACC)biasvolt - (ACC)yj, u, dw[(size_t)I * J + j]);
+        if (dw_abs) dw_abs[(size_t)I * J + j] += fabs(((double)biasvolt - (double)yj) * (double)u);
+      }
     }
   }
   return 0;
@@ -176,7 +186,7 @@ static void FN(gather_patch)(const float* x, int H, int W, int C, int Kh, int Kw
 int FN(oracle_cv_forward)(const float* x, const float* w, int B, int H, int W, int C, int Kc,
                           int Kh, int Kw, int Sh, int Sw, int pt, int pl, int Nh, int Nw,
                           float maxv, float theta, float biasvolt,
-                          ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol) {
+                          ACC* y, ACC* inv, int* kcount, unsigned char* illc, double tol, double* cond) {
   int I = Kh * Kw * C;
   float* row = (float*)malloc(sizeof(float) * (size_t)I * 3);
   int* ord = (int*)malloc(sizeof(int) * (size_t)I * 2);
@@ -188,7 +198,7 @@ int FN(oracle_cv_forward)(const float* x, const float* w, int B, int H, int W, i
         FN(gather_patch)(x, H, W, C, Kh, Kw, Sh, Sw, pt, pl, b, nh, nw, maxv, row);
         FN(sort_row)(row, I, row + I, ord, row + 2 * (size_t)I, ord + I);
         FN(row_forward)(row + I, ord, I, w, Kc, maxv, theta, biasvolt, y + r * Kc, inv + r * Kc,
-                        kcount ? kcount + r * Kc : 0, illc ? illc + r * Kc : 0, tol);
+                        kcount ? kcount + r * Kc : 0, illc ? illc + r * Kc : 0, tol, cond ? cond + r * Kc : 0);
       }
   free(row); free(ord);
   return 0;
@@ -198,7 +208,7 @@ int FN(oracle_cv_forward)(const float* x, const float* w, int B, int H, int W, i
 int FN(oracle_cv_backward)(const float* g, const float* x, const float* w, const float* yv, const float* iv,
                            int B, int H, int W, int C, int Kc, int Kh, int Kw, int Sh, int Sw,
                            int pt, int pl, int Nh, int Nw, float maxv, float biasvolt,
-                           ACC* dx, ACC* dw) {
+                           ACC* dx, ACC* dw, double* dx_abs, double* dw_abs) {
   const float maxcomp = maxv - 0.1f;
   const int bias = biasvolt > 1e-8f;
   const int I = Kh * Kw * C;
@@ -220,12 +230,16 @@ int FN(oracle_cv_backward)(const float* g, const float* x, const float* w, const
                 float xv = x[xo + c];
                 if (xv > yj) continue;
                 if (dx) dx[xo + c] = FMA_ACC(u, (ACC)w[(wo + c) * Kc + j], dx[xo + c]);
+                if (dx_abs) dx_abs[xo + c] += fabs((double)u * (double)w[(wo + c) * Kc + j]);
                 if (xv > maxcomp) continue;
                 dw[(wo + c) * Kc + j] = FMA_ACC((ACC)xv - (ACC)yj, u, dw[(wo + c) * Kc + j]);
+                if (dw_abs) dw_abs[(wo + c) * Kc + j] += fabs(((double)xv - (double)yj) * (double)u);
               }
             }
-          if (bias && !(biasvolt > yj))
+          if (bias && !(biasvolt > yj)) {
             dw[(size_t)I * Kc + j] = FMA_ACC((ACC)biasvolt - (ACC)yj, u, dw[(size_t)I * Kc + j]);
+            if (dw_abs) dw_abs[(size_t)I * Kc + j] += fabs(((double)biasvolt - (double)yj) * (double)u);
+          }
         }
   return 0;
 }

@@ -196,7 +196,8 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     for (int q = 0; q < kRT / 4; ++q) {
       const int rr = ld_r + 4 * q;
       const int r = rb + rr;
-      float xv = CUDART_INF_F, y = -CUDART_INF_F, u = 0.f;
+      // padding of the tile: x=+inf, y=0, u=0 gives min(x,y)-y = 0 and a zero product (never inf-inf)
+      float xv = CUDART_INF_F, y = 0.f, u = 0.f;
       if (r < r_end) {
         if (li < I) {
           if (!g.is_conv) {

@@ -1,8 +1,11 @@
 """Shared parity protocol of the tests (oracle = CPU restatement of the reference GPU kernels).
 
 Forward: fire/no-fire and causal-set size must agree exactly with the float64 oracle except on
-outputs the oracle flags as ill-conditioned (a fire decision within 1e-5 of flipping); spike values
-and 1/(sum w - theta) within rel 1e-4 on the rest. Backward: computed from the SAME forward output,
+outputs the oracle flags as ill-conditioned (a fire decision within 1e-5 of flipping). Spike values
+and 1/(sum w - theta): within 2e-6 of the fp32 restatement (same order of operations as the
+reference GPU kernel), and within rel max(1e-4, 4e-7*cond) of the float64 oracle, where
+cond = (theta+sum|w|)/|sum w - theta| is the factor by which fp32 rounding of the two running sums
+is amplified in y (no fp32 evaluation, the reference's included, can hold 1e-4 when cond > 100). Backward: computed from the SAME forward output,
 elementwise |a-b| <= 1e-4*|b| + 1e-5*rms(b) and relative L2 <= 1e-5 against the float64 oracle.
 """
 import numpy as np
@@ -46,10 +49,11 @@ def check_forward(y_gpu, inv_gpu, o32, o64, rows=None, maxv=1e5, what=""):
     assert ill.mean() < 0.05, "%s: %.3f of outputs flagged ill-conditioned" % (what, ill.mean())
     ok = fired_g & fired_o & ~ill
     if ok.any():
+        tol = np.maximum(REL, 4e-7 * o64["cond"][ok])
         rel = np.abs(y_gpu[ok] - o64["y"][ok]) / np.abs(o64["y"][ok])
-        assert rel.max() <= REL, "%s: spike value rel err %.3e" % (what, rel.max())
+        assert (rel / tol).max() <= 1.0, "%s: spike value rel err %.3e (%.2fx tolerance)" % (what, rel.max(), (rel / tol).max())
         reli = np.abs(inv_gpu[ok] - o64["inv"][ok]) / np.abs(o64["inv"][ok])
-        assert reli.max() <= REL, "%s: 1/wsum rel err %.3e" % (what, reli.max())
+        assert (reli / tol).max() <= 1.0, "%s: 1/wsum rel err %.3e" % (what, reli.max())
     # unfired outputs are exactly MAX with a zero reciprocal
     assert np.all(y_gpu[~fired_g] >= maxv - 0.1)
     assert np.all(inv_gpu[y_gpu >= maxv] == 0)
@@ -67,18 +71,21 @@ def check_forward(y_gpu, inv_gpu, o32, o64, rows=None, maxv=1e5, what=""):
     return dict(flagged=int(ill.sum()), fired=float(fired_g.mean()))
 
 
-def check_close(a, b, what, rel=REL, rms_atol=1e-5, l2=1e-5):
+def check_close(a, b, what, rel=REL, rms_atol=1e-5, l2=1e-5, abs_sum=None):
     a = np.asarray(a, np.float64); b = np.asarray(b, np.float64)
     assert a.shape == b.shape, "%s: shape %s vs %s" % (what, a.shape, b.shape)
     rms = np.sqrt(np.mean(b * b)) if b.size else 0.0
     err = np.abs(a - b)
     tol = rel * np.abs(b) + rms_atol * rms + 1e-30
+    if abs_sum is not None:
+        tol = tol + 1e-6 * abs_sum
     worst = (err / tol).max() if b.size else 0.0
     assert worst <= 1.0, "%s: elementwise error %.2fx tolerance (max abs %.3e, rms %.3e)" % (what, worst, err.max(), rms)
     nb = np.linalg.norm(b)
     if nb > 0:
-        r = np.linalg.norm(a - b) / nb
-        assert r <= l2, "%s: relative L2 %.3e" % (what, r)
+        bound = l2 * nb + (4e-7 * np.linalg.norm(abs_sum) if abs_sum is not None else 0.0)
+        r = np.linalg.norm(a - b)
+        assert r <= bound, "%s: L2 error %.3e vs bound %.3e (relative %.3e)" % (what, r, bound, r / nb)
 
 
 def im2col_rows(x, Kh, Kw, Sh, Sw, padding, maxv=1e5):

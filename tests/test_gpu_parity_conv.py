@@ -67,8 +67,8 @@ def test_conv_backward(case):
     gd = torch.from_numpy(g).cuda()
     dx, dw, dp = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl)
     ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
-    P.check_close(dx.cpu().numpy(), ref["dx"], "conv dX %s" % (case,))
-    P.check_close(dw.cpu().numpy(), ref["dw"], "conv dW %s" % (case,))
+    P.check_close(dx.cpu().numpy(), ref["dx"], "conv dX %s" % (case,), abs_sum=ref["dx_abs"])
+    P.check_close(dw.cpu().numpy(), ref["dw"], "conv dW %s" % (case,), abs_sum=ref["dw_abs"])
     assert np.all(dp.cpu().numpy() == 0)
     # reference convention: padded input in, padded-shape gradient out; its interior is our dx
     xp = O.pad_like_reference(x, Kh, Kw, Sh, Sw, padding)
@@ -77,5 +77,7 @@ def test_conv_backward(case):
     if padding == "SAME":
         inner = dxp[:, pt:pt + H, pl:pl + W, :]
         assert torch.equal(inner, dx)
-        assert float(dxp.abs().sum() - inner.abs().sum()) == 0.0  # padding positions get no gradient
+        rest = dxp.clone()
+        rest[:, pt:pt + H, pl:pl + W, :] = 0
+        assert float(rest.abs().max()) == 0.0  # padding positions get no gradient
     assert torch.equal(dwp, dw)
