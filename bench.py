@@ -1,0 +1,512 @@
+"""Benchmark of the SNN-TC hot path: forward+backward samples/s of an SNN-TC train step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config cifar|mnist|imagenet|dense1|conv3]
+    python bench.py --impl reference ...        # the reference's own CPU operators on the host cores
+
+One "step" is one train step (input encoding z=exp(t), forward, softmax-CE on -y, backward through
+SnnCvGrad/SnnFcGrad with every weight gradient written into one flat bucket, all-reduce of that
+bucket when N>1, Adam update) on one batch of synthetic input; for the single-layer configs it is
+the layer's forward plus backward on a seeded upstream gradient. Rank 0 prints ONE JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "snn_tc_fwd_bwd_samples_per_s"
+UNIT = "samples/s"
+
+CONFIGS = {
+    # name: (kind, per-GPU batch, description)
+    "cifar": ("net", 256, "CIFAR-shaped SNN-TC CNN train step, 32x32x3, conv 64-64 pool 128-128 pool 256-256 pool, dense 4096-512-10"),
+    "mnist": ("net", 1024, "MNIST-shaped SNN-TC MLP train step, 784-400-400-10"),
+    "imagenet": ("net", 64, "ImageNet-shaped SNN-TC CNN train step, 224x224x3"),
+    "dense1": ("layer", 256, "single SNN_dense 784->400 fwd+bwd, no bias"),
+    "conv3": ("layer", 128, "single SNN_conv 32x32x64 -> 128, 3x3 SAME fwd+bwd, no bias"),
+}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--config", default="cifar", choices=sorted(CONFIGS))
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the config's)")
+    ap.add_argument("--cpu-sample", type=int, default=0, help="samples per CPU-baseline step (default: auto)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=2)
+    return ap.parse_args()
+
+
+# ----------------------------------------------------------------------------------------------- data
+def net_spec(config):
+    from snntc_2023_b200 import nets
+    if config == "cifar":
+        return nets.CIFAR_CNN, (32, 32, 3), 10
+    if config == "mnist":
+        return nets.MNIST_MLP, (784,), 10
+    return nets.IMAGENET_CNN, (224, 224, 3), 1000
+
+
+def host_batches(config, batch, count, seed):
+    """`count` batches of spike TIMES t (the device encodes z=exp(t)) and integer labels."""
+    rng = np.random.default_rng(seed)
+    _, shape, classes = net_spec(config)
+    out = []
+    for _ in range(count):
+        t = rng.random((batch,) + shape, dtype=np.float32)
+        if config == "mnist":
+            t = (1.0 - t).astype(np.float32)  # t = 1 - pixel
+        out.append((t, rng.integers(0, classes, batch).astype(np.int64)))
+    return out
+
+
+def algorithmic_flops_per_sample(config):
+    """8*R*I*J per weighted layer (forward 3, dX 2, dW 3; I includes the bias row), no credit for
+    early exit or sentinel skipping; dX is not counted for the first layer of a network."""
+    from snntc_2023_b200 import nets
+    if config == "dense1":
+        return 8.0 * 784 * 400
+    if config == "conv3":
+        return 8.0 * 32 * 32 * 576 * 128
+    specs, shape, _ = net_spec(config)
+    return float(sum(r["R"] * r["I"] * r["J"] * (8 if r["needs_dx"] else 6) for r in nets.layer_work(specs, shape)))
+
+
+# ----------------------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.path = tempfile.mktemp(prefix="snntc_clocks_", suffix=".csv")
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                f = [c.strip() for c in line.split(",")]
+                if len(f) < 8:
+                    continue
+                try:
+                    sm.append(float(f[0])); mx.append(float(f[1]))
+                except ValueError:
+                    continue
+                for n, v in zip(names, f[4:8]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        busy = [v for v in sm if v > 0.5 * (max(mx) if mx else 1)] or sm
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------- CPU arm
+def cpu_threads():
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_step_fn(config, sample, seed):
+    """Returns (fn running one CPU step over `sample` samples, kind)."""
+    import oracle as O
+    from oracle import ref_model
+    from snntc_2023_b200 import nets
+    kind = "reference" if O.ref_lib() is not None else "port"
+    threads = cpu_threads()
+    rng = np.random.default_rng(seed)
+    if config in ("dense1", "conv3"):
+        if config == "dense1":
+            x = np.exp(rng.random((sample, 784))).astype(np.float32)
+            w = rng.normal(2 / 784, 1 / 28, (784, 400)).astype(np.float32)
+            p = O.fc_params(biasvolt=0.0)
+            g = rng.standard_normal((sample, 400)).astype(np.float32)
+        else:
+            x = np.exp(rng.random((sample, 32, 32, 64))).astype(np.float32)
+            w = rng.normal(2 / 576, 1 / 24, (576, 128)).astype(np.float32)
+            p = O.cv_params(3, 3, 1, 1, "SAME", 0.0)
+            g = rng.standard_normal((sample, 32, 32, 128)).astype(np.float32)
+        bounds = np.linspace(0, sample, min(threads, sample) + 1).astype(int)
+
+        def one(a, b):
+            xs, gs = x[a:b], g[a:b]
+            g2 = np.concatenate([gs, np.zeros_like(gs)])
+            if kind == "reference" and config == "dense1":
+                out = O.ref_fc_forward(xs, w, p)
+                O.ref_fc_backward(g2, xs, w, p, out)
+            elif kind == "reference":
+                xp = O.pad_like_reference(xs, 3, 3, 1, 1, "SAME")
+                y = O.ref_cv_forward(xp, w, p)
+                O.ref_cv_backward(g2, xp, w, p, np.concatenate([y, np.zeros_like(y)]))
+            elif config == "dense1":
+                o = O.fc_forward(xs, w, p, "f32"); O.fc_backward(gs, xs, w, p, o["y"], o["inv"], "f32")
+            else:
+                o = O.cv_forward(xs, w, p, "f32"); O.cv_backward(gs, xs, w, p, o["y"], o["inv"], "f32")
+
+        def fn():
+            from concurrent.futures import ThreadPoolExecutor
+            with ThreadPoolExecutor(max(1, len(bounds) - 1)) as ex:
+                list(ex.map(lambda ab: one(*ab), [(a, b) for a, b in zip(bounds[:-1], bounds[1:]) if b > a]))
+        return fn, kind, min(threads, sample)
+    specs, shape, classes = net_spec(config)
+    weights = nets.spec_weights(specs, 1000 * (list(CONFIGS).index(config) + 1))
+    t, labels = host_batches(config, sample, 1, seed)[0]
+    x = np.exp(t)
+
+    def fn():
+        ref_model.train_step(specs, weights, x, labels, threads=threads, kind=kind)
+    return fn, kind, min(threads, sample)
+
+
+def default_cpu_sample(config):
+    per_core = {"cifar": 2, "mnist": 64, "imagenet": 1, "dense1": 64, "conv3": 1}[config]
+    return max(1, per_core * cpu_threads()) if config != "imagenet" else max(1, min(cpu_threads(), 8))
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = args.cpu_sample or default_cpu_sample(args.config)
+    fn, kind, cores = cpu_step_fn(args.config, sample, 99)
+    for _ in range(min(args.warmup, 1)):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = time.perf_counter() - t0
+    value = sample * args.steps / dt
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": 1000.0 * dt / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.config, "description": CONFIGS[args.config][2],
+                   "note": "reference CPU operators on host cores; each step is a bounded sample of the workload"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": "%d samples per step, batch split over %d threads" % (sample, cores)},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------- GPU arm
+class NetWorkload:
+    def __init__(self, config, batch, device, world):
+        import torch
+        from snntc_2023_b200 import nets
+        self.torch = torch
+        self.config, self.batch, self.device, self.world = config, batch, device, world
+        specs, shape, classes = net_spec(config)
+        weights = nets.spec_weights(specs, 1000 * (list(CONFIGS).index(config) + 1))
+        self.net = nets.SnnNet(specs, weights=weights, device=device)
+        self.flat = torch.nn.Parameter(self.net.flat_param)
+        self.flat.grad = self.net.flat_grad
+        self.opt = torch.optim.Adam([self.flat], lr=1e-5, fused=True)
+        self.h2d_bytes = batch * int(np.prod(shape)) * 4 + batch * 8
+        self.d2h_bytes = 4
+        self.optimize = True
+
+    def stage(self, host):
+        t, lab = host
+        torch = self.torch
+        return (torch.from_numpy(t).pin_memory(), torch.from_numpy(lab).pin_memory())
+
+    def to_device(self, pinned):
+        return (pinned[0].to(self.device, non_blocking=True), pinned[1].to(self.device, non_blocking=True))
+
+    def step(self, dev_batch):
+        torch = self.torch
+        t, lab = dev_batch
+        z = torch.exp(t)
+        loss = self.net.loss(z, lab)
+        loss.backward()
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(self.net.flat_grad)
+            self.net.flat_grad.mul_(1.0 / self.world)
+        if self.optimize:
+            self.opt.step()
+        return loss
+
+
+class LayerWorkload:
+    def __init__(self, config, batch, device, world):
+        import torch
+        from snntc_2023_b200 import ops
+        self.torch, self.ops = torch, ops
+        self.config, self.batch, self.device = config, batch, device
+        rng = np.random.default_rng(1000 * (list(CONFIGS).index(config) + 1))
+        if config == "dense1":
+            self.w = torch.from_numpy(rng.normal(2 / 784, 1 / 28, (784, 400)).astype(np.float32)).to(device)
+            self.params = np.array([1e5, 1e-10, 1.0, 0, 0, 0.0], np.float32)
+            self.xshape, self.gshape = (batch, 784), (batch, 400)
+        else:
+            self.w = torch.from_numpy(rng.normal(2 / 576, 1 / 24, (576, 128)).astype(np.float32)).to(device)
+            self.params = np.array([1e5, 0, 0, 1e-10, 1.0, 0, 3, 3, 1, 1, 1, 0.0], np.float32)
+            self.xshape, self.gshape = (batch, 32, 32, 64), (batch, 32, 32, 128)
+        self.h2d_bytes = int(np.prod(self.xshape)) * 4 + int(np.prod(self.gshape)) * 4
+        self.d2h_bytes = 4
+        self.optimize = False
+
+    def host_batches(self, count, seed):
+        rng = np.random.default_rng(seed)
+        return [(rng.random(self.xshape, dtype=np.float32), rng.standard_normal(self.gshape).astype(np.float32))
+                for _ in range(count)]
+
+    def stage(self, host):
+        torch = self.torch
+        return (torch.from_numpy(host[0]).pin_memory(), torch.from_numpy(host[1]).pin_memory())
+
+    def to_device(self, pinned):
+        return (pinned[0].to(self.device, non_blocking=True), pinned[1].to(self.device, non_blocking=True))
+
+    def step(self, dev_batch):
+        torch, ops = self.torch, self.ops
+        t, g = dev_batch
+        z = torch.exp(t)
+        if self.config == "dense1":
+            out = ops.snn_fc(z, self.w, self.params)
+            dx, dw, _ = ops.snn_fc_grad(g, z, self.w, self.params, out)
+        else:
+            out = ops.snn_cv(z, self.w, self.params, 1, 1, 32, 32)
+            dx, dw, _ = ops.snn_cv_grad(g, z, self.w, self.params, out, 1, 1)
+        return dw.sum() + dx.sum()
+
+
+def time_region(torch, dist, world, fn, steps):
+    """barrier + sync, `steps` calls of fn(i) between two CUDA events on the current stream, sync + barrier."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def profile_kernels(torch, wl, batches, steps, lib):
+    """Per-kernel CUDA-event timings of `steps` extra steps: forward calls as they are, backward calls
+    once with only the dX kernel and once with only the dW kernels enabled."""
+    from snntc_2023_b200 import ops
+    agg = {}
+
+    def run(mask):
+        lib.snntc_profile_backward_parts(mask)
+        ops.Profile.records = []
+        opt = wl.optimize
+        wl.optimize = False
+        for i in range(steps):
+            wl.step(batches[i % len(batches)])
+        torch.cuda.synchronize()
+        wl.optimize = opt
+        recs = ops.Profile.records
+        ops.Profile.records = None
+        lib.snntc_profile_backward_parts(3)
+        return recs
+
+    for mask, part in ((1, "dx"), (2, "dw")):
+        for tag, dims, e0, e1 in run(mask):
+            ms = e0.elapsed_time(e1)
+            if tag.endswith("forward"):
+                if mask != 1:
+                    continue
+                key, flops = ("forward", tag[:2]) + tuple(dims[:3]), 3.0 * dims[0] * dims[1] * dims[2]
+            else:
+                if part == "dx" and not dims[3]:
+                    continue
+                key = (part, tag[:2]) + tuple(dims[:3])
+                flops = (2.0 if part == "dx" else 3.0) * dims[0] * dims[1] * dims[2]
+            a = agg.setdefault(key, [0.0, 0, flops])
+            a[0] += ms; a[1] += 1
+    return agg
+
+
+def measure_fp32_peak(torch, lib):
+    import ctypes
+    sink = torch.zeros(4, device="cuda")
+    flops = ctypes.c_double(0)
+    stream = torch.cuda.current_stream().cuda_stream
+    best = 0.0
+    for it in range(4):
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = lib.snntc_fp32_probe(sink.data_ptr(), 1 << 15, 148 * 8, ctypes.byref(flops), stream)
+        e1.record()
+        torch.cuda.synchronize()
+        if rc != 0:
+            return None
+        if it > 0:
+            best = max(best, flops.value / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return best
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from snntc_2023_b200 import _lib
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the SNN-TC operators have no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    kind, def_batch, desc = CONFIGS[args.config]
+    batch = args.batch or def_batch
+    wl = (NetWorkload if kind == "net" else LayerWorkload)(args.config, batch, device, world)
+    nb = 4
+    seed = 1000 * (list(CONFIGS).index(args.config) + 1) + rank
+    hosts = host_batches(args.config, batch, nb, seed) if kind == "net" else wl.host_batches(nb, seed)
+    pinned = [wl.stage(h) for h in hosts]
+    resident = [wl.to_device(p) for p in pinned]
+    torch.cuda.synchronize()
+
+    # warm-up (also sizes the caching allocator)
+    for i in range(max(args.warmup, 3)):
+        wl.step(resident[i % nb])
+    torch.cuda.synchronize()
+
+    # ---- device-resident throughput
+    sampler = ClockSampler(local) if rank == 0 else None
+    l0 = lib.snntc_launch_count()
+    ms = time_region(torch, dist, world, lambda i: wl.step(resident[i % nb]), args.steps)
+    launches = lib.snntc_launch_count() - l0
+    clocks = sampler.stop() if sampler else None
+    value = batch * world * args.steps / (ms * 1e-3)
+
+    # ---- end to end: pinned host -> device every step, loss read back every step
+    def e2e_step(i):
+        b = wl.to_device(pinned[i % nb])
+        float(wl.step(b).item())
+    for i in range(2):
+        e2e_step(i)
+    ms_e2e = time_region(torch, dist, world, e2e_step, args.steps)
+    e2e_value = batch * world * args.steps / (ms_e2e * 1e-3)
+
+    line = None
+    if rank == 0:
+        flops_sample = algorithmic_flops_per_sample(args.config)
+        fp32_peak = measure_fp32_peak(torch, lib)
+        agg = profile_kernels(torch, wl, resident, max(1, args.profile_steps), lib)
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        hbm_peak, hbm_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+        # group by kernel kind, find the dominant one
+        kinds = {}
+        layers = []
+        psteps = max(1, args.profile_steps)
+        for key, (tms, n, flops) in sorted(agg.items()):
+            per_step = n / psteps  # launches of this shape per step
+            k = kinds.setdefault(key[0], [0.0, 0.0, 0])
+            k[0] += tms / psteps; k[1] += flops * per_step; k[2] += per_step
+            layers.append({"kernel": key[0], "op": key[1], "R": key[2], "I": key[3], "J": key[4],
+                           "ms": tms / n, "tflops": flops / (tms / n * 1e-3) / 1e12})
+        total_ms = sum(v[0] for v in kinds.values()) or 1.0
+        dom = max(kinds, key=lambda k: kinds[k][0])
+        dms, dflops, dn = kinds[dom]
+        names = {"forward": "snn_forward_kernel", "dx": "snn_dx_kernel", "dw": "snn_dw_kernel(+reduce)"}
+        traffic = None
+        try:
+            traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(args.config, {}).get(dom)
+        except Exception:
+            pass
+        achieved = dflops / (dms * 1e-3) / 1e12
+        roofline = {
+            "bound": "fp32", "kernel": names[dom], "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
+            "frac": (achieved / fp32_peak) if fp32_peak else None, "traffic": traffic,
+            "peak_source": "FMA-only probe kernel timed in this run (MEASURED_PEAKS.json holds no FP32 figure)",
+            "launches_per_step": dn, "ms_per_step": dms, "share_of_kernel_time": dms / total_ms,
+            "kernel_shares": {names[k]: v[0] / total_ms for k, v in kinds.items()},
+            "step": {"algorithmic_tflops": flops_sample * batch / (ms / args.steps * 1e-3) / 1e12,
+                     "frac_of_fp32_peak": (flops_sample * batch / (ms / args.steps * 1e-3) / 1e12 / fp32_peak) if fp32_peak else None},
+            "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src, "layers": layers,
+        }
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            sample = args.cpu_sample or default_cpu_sample(args.config)
+            fn, ckind, cores = cpu_step_fn(args.config, sample, 99)
+            t0 = time.perf_counter(); reps = 0
+            while True:
+                fn(); reps += 1
+                if time.perf_counter() - t0 > 10.0 or reps >= 3:
+                    break
+            dt = time.perf_counter() - t0
+            cpu = {"value": sample * reps / dt, "unit": UNIT, "cores": cores, "kind": ckind,
+                   "sample": "%d samples per step x %d steps, batch split over %d threads" % (sample, reps, cores)}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.config, "description": desc, "per_gpu_batch": batch, "global_batch": batch * world,
+                       "parallelism": "dp%d" % world, "weights": "reference init randn*sqrt(15/fan_in), zero bias row" if kind == "net" else "N(2/I,1/I), no bias",
+                       "l2": "4 rotating input batches; activations of the conv layers exceed the 126 MB L2",
+                       "optimizer": "Adam (fused, flat parameter buffer)" if kind == "net" else None},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+        }
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

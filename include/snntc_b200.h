@@ -115,6 +115,19 @@ SNNTC_API int snntc_minpool_forward(const float* x_nhwc, float* y, int* arg, int
 SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx, size_t n_out, size_t n_in,
                                      void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Measurement helpers (no counterpart in the reference).
+ *   snntc_launch_count            kernels launched by this library since it was loaded
+ *   snntc_profile_backward_parts  bit 0: run the dX kernel, bit 1: run the dW kernels (default 3);
+ *                                 lets a profiler time the two halves of a backward call apart
+ *   snntc_fp32_probe              queues `ctas` CTAs of 256 threads running `iters` rounds of 8
+ *                                 independent FMAs each and reports the flop count: timed by the
+ *                                 caller, it gives the FP32 issue ceiling the kernels are judged against
+ */
+SNNTC_API unsigned long long snntc_launch_count(void);
+SNNTC_API void snntc_profile_backward_parts(int mask);
+SNNTC_API int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

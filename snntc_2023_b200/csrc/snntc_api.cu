@@ -7,6 +7,15 @@
 #include <limits.h>
 #include <string.h>
 
+#include <atomic>
+
+namespace snntc {
+static std::atomic<unsigned long long> g_launches{0};
+static std::atomic<int> g_backward_parts{3};
+void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
+int backward_parts() { return g_backward_parts.load(std::memory_order_relaxed); }
+}  // namespace snntc
+
 namespace {
 
 thread_local char g_cuda_err[256] = "";
@@ -141,6 +150,36 @@ const char* snntc_status_string(int status) {
 const char* snntc_last_cuda_error(void) { return g_cuda_err; }
 
 const char* snntc_version(void) { return "snntc_b200 0.1 sm_100a"; }
+
+unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std::memory_order_relaxed); }
+
+void snntc_profile_backward_parts(int mask) { snntc::g_backward_parts.store(mask & 3, std::memory_order_relaxed); }
+
+namespace {
+// independent FMA chains, nothing else: the FP32 issue ceiling a masked-FMA kernel is judged against
+__global__ void __launch_bounds__(256) fp32_probe_kernel(float* sink, int iters, float a, float b) {
+  float v[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) v[k] = (float)(threadIdx.x + k);
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = fmaf(v[k], a, b);
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += v[k];
+  if (s == 12345.678f) sink[0] = s;  // keeps the chains alive without a store in practice
+}
+}  // namespace
+
+int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream) {
+  if (!sink || !flops_out) return SNNTC_E_NULL;
+  if (iters <= 0 || ctas <= 0) return SNNTC_E_SHAPE;
+  fp32_probe_kernel<<<ctas, 256, 0, (cudaStream_t)stream>>>(sink, iters, 0.999f, 0.001f);
+  snntc::count_launch();
+  *flops_out = 2.0 * 8.0 * (double)iters * 256.0 * (double)ctas;
+  return cudaGetLastError() == cudaSuccess ? SNNTC_OK : SNNTC_E_CUDA;
+}
 
 size_t snntc_fc_forward_workspace_bytes(int B, int I, int J) {
   snntc::Geometry g; memset(&g, 0, sizeof(g));

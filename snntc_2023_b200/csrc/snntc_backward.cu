@@ -290,13 +290,16 @@ size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
                     float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, cudaStream_t s) {
   const int Itot = g.I + g.has_bias;
-  if (dx) {
+  const int parts = backward_parts();
+  if (dx && (parts & 1)) {
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
     snn_dx_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, w, out, dx);
+    count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
+  if (!(parts & 2)) return OK;
   const DwPlan p = plan_dw(g, li);
   float* partial = dw;
   if (p.splits > 1) {
@@ -306,12 +309,14 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   }
   dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTile - 1) / kTile, p.splits);
   snn_dw_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, out, partial, p.rows_per_split);
+  count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (p.splits > 1) {
     const size_t n = (size_t)Itot * g.J;
     int blocks = (int)((n + 255) / 256);
     if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
     snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, p.splits);
+    count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
   return OK;

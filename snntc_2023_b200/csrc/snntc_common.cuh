@@ -25,6 +25,11 @@ struct LaunchInfo {
   int max_smem_optin;  // bytes of dynamic shared memory one CTA may opt in to
 };
 
+// number of kernels this library has launched since it was loaded (read by snntc_launch_count)
+void count_launch(int n = 1);
+// profiling aid: bit 0 = run the dX kernel, bit 1 = run the dW kernels (default 3)
+int backward_parts();
+
 // status codes mirrored from include/snntc_b200.h
 enum { OK = 0, E_UNSUPPORTED = -6, E_CUDA = -7 };
 

@@ -252,6 +252,7 @@ int launch_t(const Geometry& g, const float* x, const float* w, float* out, cons
   int grid = li.num_sms * ctas_per_sm;
   if (grid > groups) grid = groups;
   kern<<<grid, kFwdThreads, smem, s>>>(g, x, w, out, rt, npad < 2 ? 2 : npad, log2_half);
+  count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
 

@@ -5,6 +5,8 @@
 
 #include <cuda_runtime.h>
 
+namespace snntc { void count_launch(int n = 1); }
+
 namespace {
 
 __global__ void minpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int* __restrict__ arg,
@@ -69,6 +71,7 @@ int snntc_minpool_forward(const float* x, float* y, int* arg, int B, int H, int 
   const size_t n = (size_t)B * Nh * Nw * C;
   minpool_fwd_kernel<<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(x, y, arg, B, H, W, C, Kh, Kw, Sh, Sw, pad_top,
                                                                      pad_left, Nh, Nw, padvalue);
+  snntc::count_launch();
   return cudaGetLastError() == cudaSuccess ? SNNTC_OK : SNNTC_E_CUDA;
 }
 
@@ -77,6 +80,7 @@ int snntc_minpool_backward(const float* gy, const int* arg, float* dx, size_t n_
   if (n_out == 0 || n_in == 0) return SNNTC_E_SHAPE;
   if (cudaMemsetAsync(dx, 0, n_in * sizeof(float), (cudaStream_t)stream) != cudaSuccess) return SNNTC_E_CUDA;
   minpool_bwd_kernel<<<grid_for(n_out), 256, 0, (cudaStream_t)stream>>>(gy, arg, dx, n_out);
+  snntc::count_launch();
   return cudaGetLastError() == cudaSuccess ? SNNTC_OK : SNNTC_E_CUDA;
 }
 

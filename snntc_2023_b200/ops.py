@@ -22,6 +22,29 @@ import torch
 from . import _lib
 
 
+# ------------------------------------------------------------------------------------------ profiling hook
+class Profile:
+    """When `Profile.records` is a list, every library call appends (tag, dims, start_event, end_event)
+    recorded on the calling stream; used by bench.py to time the kernels of a step one by one."""
+    records = None
+
+    @staticmethod
+    def begin(t):
+        if Profile.records is None:
+            return None
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(t.device))
+        return ev
+
+    @staticmethod
+    def end(ev, t, tag, dims):
+        if ev is None:
+            return
+        ev1 = torch.cuda.Event(enable_timing=True)
+        ev1.record(torch.cuda.current_stream(t.device))
+        Profile.records.append((tag, dims, ev, ev1))
+
+
 # ------------------------------------------------------------------------------------------ helpers
 def _as_cuda_f32(t, name):
     if not isinstance(t, torch.Tensor):
@@ -87,8 +110,10 @@ def snn_fc(inp, weight, params):
     with torch.cuda.device(x.device):
         out = torch.empty((2 * B, J), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
+        ev = Profile.begin(x)
         rc = lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
                                   _ptr(ws), wsb, _stream(x))
+        Profile.end(ev, x, "fc_forward", (B, rows, J))
     _lib.check(rc, "SnnFc")
     return out
 
@@ -109,8 +134,10 @@ def snn_fc_grad(grad, inp, weight, params, oldout, need_input_grad=True, grad_we
         dw = grad_weight_out if grad_weight_out is not None else torch.empty_like(w)
         dp = torch.empty(6, dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_fc_backward_workspace_bytes(B, I, rows, J), x.device)
+        ev = Profile.begin(x)
         rc = lib.snntc_fc_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
                                    _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, I, rows, J, _ptr(ws), wsb, _stream(x))
+        Profile.end(ev, x, "fc_backward", (B, rows, J, need_input_grad))
     _lib.check(rc, "SnnFcGrad")
     return dx, dw, dp
 
@@ -139,8 +166,10 @@ def snn_cv(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
     with torch.cuda.device(x.device):
         out = torch.empty((2 * B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
+        ev = Profile.begin(x)
         rc = lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
                                   pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
+        Profile.end(ev, x, "cv_forward", (B * Nh * Nw, rows, Kc))
     _lib.check(rc, "SnnCv")
     return out
 
@@ -162,9 +191,11 @@ def snn_cv_grad(grad, inp, weight, params, oldout, pad_top=0, pad_left=0, need_i
         dw = grad_weight_out if grad_weight_out is not None else torch.empty_like(w)
         dp = torch.empty(12, dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_cv_backward_workspace_bytes(B, H, W, C, rows, Kc, Nh, Nw), x.device)
+        ev = Profile.begin(x)
         rc = lib.snntc_cv_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
                                    _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, H, W, C, rows, Kc, pt, pl, Nh, Nw,
                                    _ptr(ws), wsb, _stream(x))
+        Profile.end(ev, x, "cv_backward", (B * Nh * Nw, rows, Kc, need_input_grad))
     _lib.check(rc, "SnnCvGrad")
     return dx, dw, dp
 
