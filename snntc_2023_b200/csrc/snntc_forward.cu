@@ -1,12 +1,19 @@
 // SNN-TC forward (SnnFc / SnnCv) for sm_100a: gather -> sort in shared memory -> sorted walk.
 //
-// One CTA takes a group of rows (dense samples or conv receptive fields, gathered straight from the
-// NHWC image with MAX outside it), packs each element as (sortable value bits << 32 | source index),
-// sorts every row of the group in shared memory with a bitonic network that needs no power-of-two
-// padding, and then lets each warp walk one row for 32*JPT outputs: lanes span consecutive output
-// columns so every weight-row read is one coalesced 128-byte line. The walk keeps the running
-// sum(w)-theta and sum(w*x) per output in registers in sorted order, bias first, and applies the
-// division-free causality test of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69).
+// Rows are dense samples or conv receptive fields (gathered straight from the NHWC image with MAX
+// outside it). Two kernels, joined by a scratch buffer of sorted keys in global memory:
+//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest are packed as
+//      (sortable value bits << 32 | source index) in shared memory while four 8-bit digit histograms
+//      of the value bits are built;
+//   2. sort: a stable least-significant-digit radix sort by the warp (digit passes in which every key
+//      falls in one bin are skipped), O(n) per row; rows of <= 32 inputs are ranked with shuffles,
+//      rows too long for two shared-memory buffers fall back to an in-place bitonic network;
+//   3. walk (walk kernel): every warp takes (row, block of 32*JPT outputs) items; lanes span
+//      consecutive output columns so each weight-row read is one coalesced 128-byte line. The running
+//      sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the arithmetic
+//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69). Steps are taken eight at a time
+//      while only watching for a sign change of ysum - x*wsum; when one shows up, the eight steps are
+//      replayed with the reference's exact division-free causality test.
 #include "snntc_common.cuh"
 
 namespace snntc {
@@ -15,17 +22,16 @@ namespace {
 
 constexpr int kFwdThreads = 256;
 constexpr int kFwdWarps = kFwdThreads / 32;
-constexpr int kMaxRowsPerPass = 32;
-constexpr int kUnroll = 4;
+constexpr int kMaxRowsPerPass = 16;
+constexpr int kChunk = 8;
+constexpr int kHistWords = 4 * 256;  // per warp
 
 typedef unsigned long long u64;
 
-__device__ __forceinline__ void compare_exchange(u64* a, u64* b) {
-  u64 va = *a, vb = *b;
-  if (va > vb) { *a = vb; *b = va; }
-}
+__device__ __forceinline__ float key_value(u64 e) { return sortable_to_float((uint32_t)(e >> 32)); }
 
-// One step of the walk for one output: test "fire before consuming x", else consume (x, wv).
+// ------------------------------------------------------------------------------------------- walk
+// exact step (reference semantics): test "fire before consuming x", else consume (x, wv)
 __device__ __forceinline__ void walk_step(float x, float wv, float& wsum, float& ysum, bool& armed, bool& live) {
   if (live) {
     float wa = fabsf(wsum);
@@ -42,7 +48,14 @@ __device__ __forceinline__ void walk_step(float x, float wv, float& wsum, float&
   }
 }
 
-template <int JPT>
+// "ysum/wsum > c" without a division, as the reference evaluates it after consuming input c
+__device__ __forceinline__ bool ratio_gt(float ysum, float wsum, float c) {
+  const float wa = fabsf(wsum);
+  const float ya = wsum < 0.f ? -ysum : ysum;
+  return ya > c * wa;
+}
+
+template <int JPT, bool FULL>
 __device__ __forceinline__ void walk_row(const Geometry& g, const u64* __restrict__ keys, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
                                          float* __restrict__ y_row, float* __restrict__ inv_row) {
@@ -50,57 +63,117 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const u64* __restric
   int jl[JPT];
   bool jok[JPT];
   float wsum[JPT], ysum[JPT];
-  bool armed[JPT], live[JPT];
+  bool armed0[JPT], armed[JPT], live[JPT];
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
-    int j = jbase + lane + 32 * m;
-    jok[m] = j < J;
+    const int j = jbase + lane + 32 * m;
+    jok[m] = FULL || j < J;
     jl[m] = jok[m] ? j : J - 1;
     wsum[m] = -g.theta;
     ysum[m] = 0.f;
-    armed[m] = false;
+    armed0[m] = false;
     live[m] = true;
     if (g.has_bias) {  // the bias input (value biasvolt, weight row I) is always consumed first
-      float wb = __ldg(w + (size_t)g.I * J + jl[m]);
+      const float wb = __ldg(w + (size_t)g.I * J + jl[m]);
       wsum[m] += wb;
       ysum[m] = g.biasvolt * wb;
-      float wa = fabsf(wsum[m]);
-      float ya = wsum[m] < 0.f ? -ysum[m] : ysum[m];
-      armed[m] = ya > wa * g.biasvolt;
+      armed0[m] = ratio_gt(ysum[m], wsum[m], g.biasvolt);
     }
+    armed[m] = armed0[m];
   }
 
+  // d = ysum - x*wsum just before consuming x. A fire at step k means "ysum/wsum > previous input"
+  // held after step k-1 and "ysum/wsum <= x" holds now, i.e. d changed sign between the two steps
+  // (in exact arithmetic the first is sign(wsum)*d_{k-1} > 0 with the sums of step k, the second
+  // sign(wsum)*d_k <= 0). The speculative pass therefore only tracks sign changes of d; the exact
+  // replay below then decides with the reference's own rounded comparisons. The two can disagree only
+  // when |d| is within a few ulps of zero (a spike time tied with an input to the last bits).
+  float dprev[JPT];
+  bool first = true;
   int k = 0;
   bool all_done = false;
-  for (; k + kUnroll <= nvalid && !all_done; k += kUnroll) {
-    float xs[kUnroll];
-    float wv[kUnroll][JPT];
+  for (; k + kChunk <= nvalid && !all_done; k += kChunk) {
+    float ws0[JPT], ys0[JPT];
+    int acc[JPT];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      u64 e = keys[k + u];
-      xs[u] = sortable_to_float((uint32_t)(e >> 32));
+    for (int m = 0; m < JPT; ++m) { ws0[m] = wsum[m]; ys0[m] = ysum[m]; acc[m] = 0; }
+    if (first) {
+      const float x0 = key_value(keys[0]);
+#pragma unroll
+      for (int m = 0; m < JPT; ++m) {
+        dprev[m] = fmaf(-x0, wsum[m], ysum[m]);
+        if (armed0[m]) acc[m] = -1;  // bias alone may already fire: take the first steps exactly
+      }
+      first = false;
+    }
+
+#pragma unroll
+    for (int u = 0; u < kChunk; ++u) {
+      const u64 e = keys[k + u];
+      const float x = key_value(e);
       const float* wrow = w + (size_t)(uint32_t)e * J;
 #pragma unroll
-      for (int m = 0; m < JPT; ++m) wv[u][m] = __ldg(wrow + jl[m]);
+      for (int m = 0; m < JPT; ++m) {
+        const float wv = FULL ? __ldg(wrow + jbase + lane + 32 * m) : __ldg(wrow + jl[m]);
+        const float d = fmaf(-x, wsum[m], ysum[m]);
+        acc[m] |= __float_as_int(d) ^ __float_as_int(dprev[m]);
+        dprev[m] = d;
+        wsum[m] += wv;
+        ysum[m] = fmaf(x, wv, ysum[m]);
+      }
+    }
+
+    bool flag[JPT];
+    bool need = false;
+#pragma unroll
+    for (int m = 0; m < JPT; ++m) {
+      flag[m] = (acc[m] < 0) && live[m];
+      need |= flag[m];
+      if (!live[m]) { wsum[m] = ws0[m]; ysum[m] = ys0[m]; }  // finished outputs keep their sums
+    }
+    if (__any_sync(0xffffffffu, need)) {
+      // ---- exact replay of these eight steps for the outputs whose test tripped
+      const float xprev = k > 0 ? key_value(keys[k - 1]) : 0.f;
+#pragma unroll
+      for (int m = 0; m < JPT; ++m) {
+        if (flag[m]) {
+          wsum[m] = ws0[m];
+          ysum[m] = ys0[m];
+          armed[m] = k > 0 ? ratio_gt(ysum[m], wsum[m], xprev) : armed0[m];
+        }
+      }
+      for (int u = 0; u < kChunk; ++u) {
+        const u64 e = keys[k + u];
+        const float x = key_value(e);
+        const float* wrow = w + (size_t)(uint32_t)e * J;
+#pragma unroll
+        for (int m = 0; m < JPT; ++m) {
+          if (flag[m]) {
+            const float wv = __ldg(wrow + jl[m]);
+            walk_step(x, wv, wsum[m], ysum[m], armed[m], live[m]);
+          }
+        }
+      }
     }
     bool any_live = false;
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) walk_step(xs[u], wv[u][m], wsum[m], ysum[m], armed[m], live[m]);
-    }
 #pragma unroll
     for (int m = 0; m < JPT; ++m) any_live |= live[m];
     all_done = !__any_sync(0xffffffffu, any_live);
   }
+
   if (!all_done) {
+    // ---- tail (fewer than eight inputs left): exact steps
+    const float xprev = k > 0 ? key_value(keys[k - 1]) : 0.f;
+#pragma unroll
+    for (int m = 0; m < JPT; ++m)
+      if (live[m]) armed[m] = k > 0 ? ratio_gt(ysum[m], wsum[m], xprev) : armed0[m];
     for (; k < nvalid; ++k) {
-      u64 e = keys[k];
-      float x = sortable_to_float((uint32_t)(e >> 32));
+      const u64 e = keys[k];
+      const float x = key_value(e);
       const float* wrow = w + (size_t)(uint32_t)e * J;
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
-        float wv = __ldg(wrow + jl[m]);
+        const float wv = __ldg(wrow + jl[m]);
         walk_step(x, wv, wsum[m], ysum[m], armed[m], live[m]);
       }
     }
@@ -108,163 +181,293 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const u64* __restric
 
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
+    // an output that stopped has fired; one that consumed every input fires iff it is armed
+    const bool fired = !live[m] || armed[m];
     float yv = g.maxv, iv = 0.f;
-    if (armed[m]) {
+    if (fired) {
       iv = __fdividef(1.0f, wsum[m]);
       yv = ysum[m] * iv;
       if (yv >= g.maxv) { yv = g.maxv; iv = 0.f; }
     }
     if (jok[m]) {
-      int j = jbase + lane + 32 * m;
+      const int j = jbase + lane + 32 * m;
       y_row[j] = yv;
       inv_row[j] = iv;
     }
   }
 }
 
-template <int JPT>
+// ------------------------------------------------------------------------------------------- gather
+// Loads one row, drops inputs above MAX-0.1, writes packed keys to dst[0..n) in index order and
+// (if hist != nullptr) counts the four 8-bit digits of every kept key. Returns n. One warp.
+__device__ __forceinline__ int gather_row(const Geometry& g, const float* __restrict__ x, int r, int lane,
+                                          u64* __restrict__ dst, unsigned* __restrict__ hist) {
+  const int I = g.I;
+  const float maxcomp = g.maxv - 0.1f;
+  int n = 0;
+  int b = 0, h0 = 0, w0 = 0;
+  const float* xr = x + (size_t)r * I;
+  if (g.is_conv) {
+    const int nw = r % g.Nw;
+    const int t = r / g.Nw;
+    const int nh = t % g.Nh;
+    b = t / g.Nh;
+    h0 = nh * g.Sh - g.pad_top;
+    w0 = nw * g.Sw - g.pad_left;
+  }
+  for (int i0 = 0; i0 < I; i0 += 32) {
+    const int i = i0 + lane;
+    float v = g.maxv;
+    if (i < I) {
+      if (!g.is_conv) {
+        v = __ldg(xr + i);
+      } else {
+        const int tap = i / g.C, c = i - tap * g.C;
+        const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
+        const int h = h0 + kh, ww = w0 + kw;
+        if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v = __ldg(x + (((size_t)b * g.H + h) * g.W + ww) * g.C + c);
+      }
+    }
+    const bool keep = (i < I) && !(v > maxcomp);
+    const unsigned mask = __ballot_sync(0xffffffffu, keep);
+    if (keep) {
+      const uint32_t key = float_to_sortable(v);
+      dst[n + __popc(mask & ((1u << lane) - 1u))] = ((u64)key << 32) | (uint32_t)i;
+      if (hist) {
+        atomicAdd(&hist[key & 255u], 1u);
+        atomicAdd(&hist[256 + ((key >> 8) & 255u)], 1u);
+        atomicAdd(&hist[512 + ((key >> 16) & 255u)], 1u);
+        atomicAdd(&hist[768 + (key >> 24)], 1u);
+      }
+    }
+    n += __popc(mask);
+  }
+  return n;
+}
+
+// ------------------------------------------------------------------------------------------- sorts
+// n <= 32: rank every key against the others with shuffles. src -> dst, one warp.
+__device__ __forceinline__ void sort_small(const u64* __restrict__ src, u64* __restrict__ dst, int n, int lane) {
+  const u64 e = lane < n ? src[lane] : ~0ull;
+  int rank = 0;
+  for (int j = 0; j < n; ++j) {
+    const u64 o = __shfl_sync(0xffffffffu, e, j);
+    rank += o < e;  // keys are unique (the index is part of them)
+  }
+  if (lane < n) dst[rank] = e;
+}
+
+// Stable LSD radix sort of n keys by their upper 32 bits, 8 bits per pass, one warp. hist holds the
+// four digit histograms on entry. Returns the buffer that holds the sorted keys.
+__device__ __forceinline__ u64* radix_sort_row(u64* a, u64* b, int n, unsigned* hist, int lane) {
+  u64* src = a;
+  u64* dst = b;
+  const unsigned lt = (1u << lane) - 1u;
+#pragma unroll 1
+  for (int p = 0; p < 4; ++p) {
+    unsigned* h = hist + 256 * p;
+    // exclusive scan of the 256 bins (8 per lane); a pass whose keys all share one digit is skipped
+    unsigned c[8], s = 0;
+    bool single = false;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { c[q] = h[lane * 8 + q]; single |= (c[q] == (unsigned)n); s += c[q]; }
+    if (__any_sync(0xffffffffu, single)) continue;
+    unsigned incl = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    unsigned run = incl - s;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) { h[lane * 8 + q] = run; run += c[q]; }
+    __syncwarp();
+    const int shift = 32 + 8 * p;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+      const int i = i0 + lane;
+      const bool act = i < n;
+      const u64 e = act ? src[i] : 0ull;
+      const unsigned d = act ? (unsigned)(e >> shift) & 255u : 256u + (unsigned)lane;
+      const unsigned peers = __match_any_sync(0xffffffffu, d);
+      const unsigned before = peers & lt;
+      unsigned off = 0;
+      if (act) off = h[d];
+      __syncwarp();
+      if (act && before == 0) h[d] = off + __popc(peers);
+      __syncwarp();
+      if (act) dst[off + __popc(before)] = e;
+    }
+    __syncwarp();
+    u64* t = src; src = dst; dst = t;
+  }
+  return src;
+}
+
+// In-place bitonic network for rows too long for two buffers; all threads of the CTA, one row.
+// Every compare-exchange moves the smaller key to the lower index, so the virtual +inf elements at
+// positions >= n never move and need no storage.
+__device__ __forceinline__ void bitonic_sort_cta(u64* keys, int n, int tid) {
+  int npad = 2;
+  while (npad < n) npad <<= 1;
+  const int half = npad >> 1;
+  for (int k = 2; k <= npad; k <<= 1) {
+    const int hk = k >> 1;
+    for (int q = tid; q < half; q += kFwdThreads) {
+      const int o = q & (hk - 1);
+      const int base = (q - o) << 1;
+      const int i = base + o, p = base + k - 1 - o;
+      if (p < n) { const u64 va = keys[i], vb = keys[p]; if (va > vb) { keys[i] = vb; keys[p] = va; } }
+    }
+    __syncthreads();
+    for (int j = hk >> 1; j >= 1; j >>= 1) {
+      for (int q = tid; q < half; q += kFwdThreads) {
+        const int o = q & (j - 1);
+        const int i = ((q - o) << 1) + o, p = i + j;
+        if (p < n) { const u64 va = keys[i], vb = keys[p]; if (va > vb) { keys[i] = vb; keys[p] = va; } }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------- kernels
+// Sort kernel: one warp per row. Shared memory per warp: two key buffers of I entries and the four
+// digit histograms. Sorted keys go to keys_g[r*istride ..], their count to nvalid_g[r].
 __global__ void __launch_bounds__(kFwdThreads)
-snn_forward_kernel(const Geometry g, const float* __restrict__ x, const float* __restrict__ w,
-                   float* __restrict__ out, int rows_per_pass, int npad, int log2_half) {
+snn_sort_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__ keys_g, int* __restrict__ nvalid_g,
+                int istride) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int I = g.I, R = g.R;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
+  unsigned char* mine = smem_raw + (size_t)warp * (2 * (size_t)I * sizeof(u64) + kHistWords * sizeof(unsigned));
+  u64* a = reinterpret_cast<u64*>(mine);
+  u64* b = a + I;
+  unsigned* hist = reinterpret_cast<unsigned*>(b + I);
+  for (int r = blockIdx.x * wpc + warp; r < R; r += gridDim.x * wpc) {
+    for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
+    __syncwarp();
+    const int n = gather_row(g, x, r, lane, a, hist);
+    __syncwarp();
+    const u64* res;
+    if (n <= 32) { sort_small(a, b, n, lane); res = b; }
+    else res = radix_sort_row(a, b, n, hist, lane);
+    __syncwarp();
+    u64* dst = keys_g + (size_t)r * istride;
+    for (int i = lane; i < n; i += 32) dst[i] = res[i];
+    if (lane == 0) nvalid_g[r] = n;
+    __syncwarp();
+  }
+}
+
+// Rows too long for two buffers per warp: one row per CTA at a time, in-place bitonic network.
+__global__ void __launch_bounds__(kFwdThreads)
+snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__ keys_g,
+                     int* __restrict__ nvalid_g, int istride) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   u64* keys = reinterpret_cast<u64*>(smem_raw);
-  __shared__ int s_nvalid[kMaxRowsPerPass];
-
-  const int I = g.I, J = g.J, R = g.R;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int num_groups = (R + rows_per_pass - 1) / rows_per_pass;
-  const int jchunks = (J + 32 * JPT - 1) / (32 * JPT);
-  const uint32_t max_key = float_to_sortable(g.maxv - 0.1f);
-  float* __restrict__ y_out = out;
-  float* __restrict__ inv_out = out + (size_t)R * J;
-
-  for (int group = blockIdx.x; group < num_groups; group += gridDim.x) {
-    const int r0 = group * rows_per_pass;
-    const int nrows = min(rows_per_pass, R - r0);
-
-    // ---- 1. gather rows into shared memory as sortable (value, index) pairs
-    for (int rr = warp; rr < nrows; rr += kFwdWarps) {
-      const int r = r0 + rr;
-      u64* krow = keys + (size_t)rr * I;
-      if (!g.is_conv) {
-        const float* xr = x + (size_t)r * I;
-        for (int i = lane; i < I; i += 32)
-          krow[i] = ((u64)float_to_sortable(__ldg(xr + i)) << 32) | (uint32_t)i;
-      } else {
-        const int nw = r % g.Nw;
-        const int t = r / g.Nw;
-        const int nh = t % g.Nh;
-        const int b = t / g.Nh;
-        const int h0 = nh * g.Sh - g.pad_top, w0 = nw * g.Sw - g.pad_left;
-        for (int i = lane; i < I; i += 32) {
-          const int tap = i / g.C, c = i - tap * g.C;
-          const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
-          const int h = h0 + kh, ww = w0 + kw;
-          float v = g.maxv;
-          if (h >= 0 && h < g.H && ww >= 0 && ww < g.W)
-            v = __ldg(x + (((size_t)b * g.H + h) * g.W + ww) * g.C + c);
-          krow[i] = ((u64)float_to_sortable(v) << 32) | (uint32_t)i;
-        }
-      }
+  __shared__ int s_n;
+  const int tid = threadIdx.x;
+  for (int r = blockIdx.x; r < g.R; r += gridDim.x) {
+    if (tid < 32) {
+      const int n = gather_row(g, x, r, tid, keys, nullptr);
+      if (tid == 0) s_n = n;
     }
     __syncthreads();
-
-    // ---- 2. bitonic sort of every row; every compare-exchange moves the smaller key to the lower
-    // index, so virtual +inf elements at positions >= I never move and need no storage.
-    {
-      const int half = npad >> 1;
-      const int total = nrows * half;
-      for (int k = 2; k <= npad; k <<= 1) {
-        const int hk = k >> 1;
-        for (int t = tid; t < total; t += kFwdThreads) {
-          const int rr = t >> log2_half, q = t & (half - 1);
-          const int o = q & (hk - 1);
-          const int base = (q - o) << 1;
-          const int i = base + o, p = base + k - 1 - o;
-          if (p < I) compare_exchange(keys + (size_t)rr * I + i, keys + (size_t)rr * I + p);
-        }
-        __syncthreads();
-        for (int j = hk >> 1; j >= 1; j >>= 1) {
-          for (int t = tid; t < total; t += kFwdThreads) {
-            const int rr = t >> log2_half, q = t & (half - 1);
-            const int o = q & (j - 1);
-            const int i = ((q - o) << 1) + o, p = i + j;
-            if (p < I) compare_exchange(keys + (size_t)rr * I + i, keys + (size_t)rr * I + p);
-          }
-          __syncthreads();
-        }
-      }
-    }
-
-    // ---- 3. inputs above MAX-0.1 never spike: the walk stops at the first of them
-    if (tid < nrows) {
-      const u64* krow = keys + (size_t)tid * I;
-      int lo = 0, hi = I;
-      while (lo < hi) {
-        int mid = (lo + hi) >> 1;
-        if ((uint32_t)(krow[mid] >> 32) <= max_key) lo = mid + 1; else hi = mid;
-      }
-      s_nvalid[tid] = lo;
-    }
-    __syncthreads();
-
-    // ---- 4. walk
-    const int items = nrows * jchunks;
-    for (int item = warp; item < items; item += kFwdWarps) {
-      const int rr = item / jchunks, jc = item - rr * jchunks;
-      const size_t r = (size_t)(r0 + rr);
-      walk_row<JPT>(g, keys + (size_t)rr * I, s_nvalid[rr], w, jc * 32 * JPT, lane, y_out + r * J, inv_out + r * J);
-    }
+    const int n = s_n;
+    bitonic_sort_cta(keys, n, tid);
+    u64* dst = keys_g + (size_t)r * istride;
+    for (int i = tid; i < n; i += kFwdThreads) dst[i] = keys[i];
+    if (tid == 0) nvalid_g[r] = n;
     __syncthreads();
   }
 }
 
-int pick_rows_per_pass(const Geometry& g, const LaunchInfo& li) {
-  const size_t per_row = (size_t)g.I * sizeof(u64);
-  const size_t budget = (size_t)li.max_smem_optin - 1024;
-  if (per_row > budget) return 0;
-  size_t soft = 96 * 1024;  // leave room for two CTAs per SM when rows are short
-  int rt = (int)((soft > per_row ? soft : per_row) / per_row);
-  if (rt > kMaxRowsPerPass) rt = kMaxRowsPerPass;
-  // do not starve the grid: aim for at least ~2 groups per SM
-  long want = ((long)g.R + 2L * li.num_sms - 1) / (2L * li.num_sms);
-  if (want < 1) want = 1;
-  if (rt > want) rt = (int)want;
-  if (rt < 1) rt = 1;
-  return rt;
+// Walk kernel: every warp takes (row, block of 32*JPT outputs) items, adjacent warps share a row.
+template <int JPT>
+__global__ void __launch_bounds__(kFwdThreads)
+snn_walk_kernel(const Geometry g, const u64* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
+                const float* __restrict__ w, float* __restrict__ out) {
+  const int J = g.J, R = g.R;
+  const int lane = threadIdx.x & 31;
+  const int jchunks = (J + 32 * JPT - 1) / (32 * JPT);
+  const bool full_j = (J % (32 * JPT)) == 0;
+  float* __restrict__ y_out = out;
+  float* __restrict__ inv_out = out + (size_t)R * J;
+  const long items = (long)R * jchunks;
+  const long wstride = (long)gridDim.x * kFwdWarps;
+  for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
+    const int r = (int)(item / jchunks), jc = (int)(item - (long)r * jchunks);
+    const u64* krow = keys_g + (size_t)r * istride;
+    const int n = __ldg(nvalid_g + r);
+    if (full_j)
+      walk_row<JPT, true>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+    else
+      walk_row<JPT, false>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+  }
 }
 
+int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of keys start 16-byte aligned
+
+size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
+
 template <int JPT>
-int launch_t(const Geometry& g, const float* x, const float* w, float* out, const LaunchInfo& li, cudaStream_t s) {
-  const int rt = pick_rows_per_pass(g, li);
-  if (rt == 0) return E_UNSUPPORTED;
-  int npad = 1, log2n = 0;
-  while (npad < g.I) { npad <<= 1; ++log2n; }
-  const int log2_half = log2n > 0 ? log2n - 1 : 0;
-  const size_t smem = (size_t)rt * g.I * sizeof(u64);
-  auto kern = snn_forward_kernel<JPT>;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)li.max_smem_optin - 1024) != cudaSuccess)
-    return E_CUDA;
-  const int groups = (g.R + rt - 1) / rt;
-  int ctas_per_sm = (int)(((size_t)li.max_smem_optin) / (smem + 2048));
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
-  if (ctas_per_sm > 4) ctas_per_sm = 4;
-  int grid = li.num_sms * ctas_per_sm;
-  if (grid > groups) grid = groups;
-  kern<<<grid, kFwdThreads, smem, s>>>(g, x, w, out, rt, npad < 2 ? 2 : npad, log2_half);
+int launch_walk(const Geometry& g, const u64* keys_g, const int* nvalid_g, const float* w, float* out,
+                const LaunchInfo& li, cudaStream_t s) {
+  const int jchunks = (g.J + 32 * JPT - 1) / (32 * JPT);
+  const long items = (long)g.R * jchunks;
+  long grid = (items + kFwdWarps - 1) / kFwdWarps;
+  const long cap = (long)li.num_sms * 8;
+  if (grid > cap) grid = cap;
+  snn_walk_kernel<JPT><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
 
 }  // namespace
 
-size_t forward_workspace_bytes(const Geometry&) { return 0; }
+size_t forward_workspace_bytes(const Geometry& g) {
+  return keys_bytes(g) + (((size_t)g.R * sizeof(int) + 15) & ~(size_t)15);
+}
 
-int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void*, size_t,
+int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void* ws, size_t ws_bytes,
                    const LaunchInfo& li, cudaStream_t s) {
-  if (g.J <= 32) return launch_t<1>(g, x, w, out, li, s);
-  if (g.J <= 64) return launch_t<2>(g, x, w, out, li, s);
-  return launch_t<4>(g, x, w, out, li, s);
+  if (!ws || ws_bytes < forward_workspace_bytes(g)) return -5;
+  u64* keys_g = static_cast<u64*>(ws);
+  int* nvalid_g = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + keys_bytes(g));
+  const int istride = key_stride(g);
+
+  // ---- sort
+  const size_t budget = (size_t)li.max_smem_optin - 1024;
+  const size_t per_warp = 2 * (size_t)g.I * sizeof(u64) + kHistWords * sizeof(unsigned);
+  if (per_warp <= budget) {
+    int wpc = (int)(budget / per_warp);
+    if (wpc > kFwdWarps) wpc = kFwdWarps;
+    // short rows: several CTAs per SM instead of one fat CTA
+    int ctas_per_sm = (int)(budget / (per_warp * wpc));
+    if (ctas_per_sm > 4) ctas_per_sm = 4;
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    const size_t smem = per_warp * wpc;
+    if (cudaFuncSetAttribute(snn_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
+      return E_CUDA;
+    long grid = ((long)g.R + wpc - 1) / wpc;
+    const long cap = (long)li.num_sms * ctas_per_sm;
+    if (grid > cap) grid = cap;
+    snn_sort_kernel<<<(int)grid, wpc * 32, smem, s>>>(g, x, keys_g, nvalid_g, istride);
+  } else {
+    const size_t smem = (size_t)g.I * sizeof(u64);
+    if (smem > budget) return E_UNSUPPORTED;
+    if (cudaFuncSetAttribute(snn_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
+      return E_CUDA;
+    int grid = g.R < li.num_sms ? g.R : li.num_sms;
+    snn_sort_long_kernel<<<grid, kFwdThreads, smem, s>>>(g, x, keys_g, nvalid_g, istride);
+  }
+  count_launch();
+  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+
+  // ---- walk
+  if (g.J <= 32) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, s);
+  if (g.J <= 64) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, s);
+  return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, s);
 }
 
 }  // namespace snntc

@@ -46,7 +46,7 @@ def check_forward(y_gpu, inv_gpu, o32, o64, rows=None, maxv=1e5, what=""):
     fired_o = o64["y"] < maxv - 0.1
     bad = (fired_g != fired_o) & ~ill
     assert bad.sum() == 0, "%s: %d fire/no-fire mismatches on well-conditioned outputs" % (what, bad.sum())
-    assert ill.mean() < 0.05, "%s: %.3f of outputs flagged ill-conditioned" % (what, ill.mean())
+    assert ill.mean() < 0.25, "%s: %.3f of outputs flagged ill-conditioned" % (what, ill.mean())
     ok = fired_g & fired_o & ~ill
     if ok.any():
         tol = np.maximum(REL, 4e-7 * o64["cond"][ok])

@@ -17,6 +17,10 @@ DENSE_CASES = [
     (16, 70, 513, 10, 1.0, "cfg"),
     (17, 33, 64, 130, 0.5, "test"),
     (18, 16, 2049, 96, 1.0, "cfg"),
+    (19, 3, 16000, 40, 1.0, "cfg"),     # too long for two shared-memory sort buffers: bitonic fallback
+    (20, 6, 4097, 512, 1.0, "cfg"),
+    (22, 40, 31, 64, 1.0, "test"),      # <= 32 inputs: shuffle rank sort
+    (23, 40, 33, 128, 0.0, "test"),
 ]
 
 
