@@ -11,9 +11,9 @@
 //   3. walk (walk kernel): every warp takes (row, block of 32*JPT outputs) items; lanes span
 //      consecutive output columns so each weight-row read is one coalesced 128-byte line. The running
 //      sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the arithmetic
-//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69). Steps are taken eight at a time
-//      while only watching for a sign change of ysum - x*wsum; when one shows up, the eight steps are
-//      replayed with the reference's exact division-free causality test.
+//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is a sign
+//      pattern of ysum - x*wsum per step, backed by the reference's exact division-free comparisons
+//      whenever the pattern shows up in any lane (see walk_row).
 #include "snntc_common.cuh"
 
 namespace snntc {
@@ -22,8 +22,6 @@ namespace {
 
 constexpr int kFwdThreads = 256;
 constexpr int kFwdWarps = kFwdThreads / 32;
-constexpr int kMaxRowsPerPass = 16;
-constexpr int kChunk = 8;
 constexpr int kHistWords = 4 * 256;  // per warp
 
 typedef unsigned long long u64;
@@ -31,39 +29,40 @@ typedef unsigned long long u64;
 __device__ __forceinline__ float key_value(u64 e) { return sortable_to_float((uint32_t)(e >> 32)); }
 
 // ------------------------------------------------------------------------------------------- walk
-// exact step (reference semantics): test "fire before consuming x", else consume (x, wv)
-__device__ __forceinline__ void walk_step(float x, float wv, float& wsum, float& ysum, bool& armed, bool& live) {
-  if (live) {
-    float wa = fabsf(wsum);
-    float ya = wsum < 0.f ? -ysum : ysum;
-    if (armed && ya <= x * wa) {
-      live = false;  // spike lies in (previous input, x]: keep the sums as they are
-    } else {
-      wsum += wv;
-      ysum = fmaf(x, wv, ysum);
-      wa = fabsf(wsum);
-      ya = wsum < 0.f ? -ysum : ysum;
-      armed = ya > x * wa;
-    }
-  }
-}
+// Entry of the sorted list handed from the sort kernel to the walk kernel: x = input value,
+// y = element offset of its weight row (source index * J).
+typedef uint2 WalkEntry;
 
 // "ysum/wsum > c" without a division, as the reference evaluates it after consuming input c
+// (snntc/snnfc_kernels.cu.cc:53-55)
 __device__ __forceinline__ bool ratio_gt(float ysum, float wsum, float c) {
   const float wa = fabsf(wsum);
   const float ya = wsum < 0.f ? -ysum : ysum;
   return ya > c * wa;
 }
+// "ysum/wsum <= c" (snntc/snnfc_kernels.cu.cc:46-48)
+__device__ __forceinline__ bool ratio_le(float ysum, float wsum, float c) {
+  const float wa = fabsf(wsum);
+  const float ya = wsum < 0.f ? -ysum : ysum;
+  return ya <= c * wa;
+}
 
-template <int JPT, bool FULL>
-__device__ __forceinline__ void walk_row(const Geometry& g, const u64* __restrict__ keys, int nvalid,
+// One warp walks one row for 32*JPT outputs (lane + 32*m). Per step and output the loop itself only
+// does the two running sums plus d = ysum - x*wsum and a sign test: a fire before consuming x means
+// "ysum/wsum > previous input" held after the previous step and "ysum/wsum <= x" holds now, which in
+// exact arithmetic is sign(wsum)*d_prev > 0 >= sign(wsum)*d. When any lane sees that pattern, the
+// warp evaluates the reference's own rounded, division-free tests for every output still running at
+// this step, so the decision is the reference's; the cheap pattern and the exact test can disagree
+// only when d is within a few ulps of zero (a spike time tied with an input to the last bits).
+template <int JPT, int CH, bool FULL>
+__device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
                                          float* __restrict__ y_row, float* __restrict__ inv_row) {
   const int J = g.J;
   int jl[JPT];
   bool jok[JPT];
-  float wsum[JPT], ysum[JPT];
-  bool armed0[JPT], armed[JPT], live[JPT];
+  float wsum[JPT], ysum[JPT], wfin[JPT], yfin[JPT], dprev[JPT];
+  int livemask[JPT];
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
     const int j = jbase + lane + 32 * m;
@@ -71,122 +70,88 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const u64* __restric
     jl[m] = jok[m] ? j : J - 1;
     wsum[m] = -g.theta;
     ysum[m] = 0.f;
-    armed0[m] = false;
-    live[m] = true;
+    bool armed0 = false;
     if (g.has_bias) {  // the bias input (value biasvolt, weight row I) is always consumed first
       const float wb = __ldg(w + (size_t)g.I * J + jl[m]);
       wsum[m] += wb;
       ysum[m] = g.biasvolt * wb;
-      armed0[m] = ratio_gt(ysum[m], wsum[m], g.biasvolt);
+      armed0 = ratio_gt(ysum[m], wsum[m], g.biasvolt);
     }
-    armed[m] = armed0[m];
+    dprev[m] = armed0 ? wsum[m] : -wsum[m];  // its sign relative to wsum says "armed before the first input"
+    wfin[m] = wsum[m];
+    yfin[m] = ysum[m];
+    livemask[m] = -1;
   }
+  float xprev = g.biasvolt;
+  bool have_prev = g.has_bias != 0;
 
-  // d = ysum - x*wsum just before consuming x. A fire at step k means "ysum/wsum > previous input"
-  // held after step k-1 and "ysum/wsum <= x" holds now, i.e. d changed sign between the two steps
-  // (in exact arithmetic the first is sign(wsum)*d_{k-1} > 0 with the sums of step k, the second
-  // sign(wsum)*d_k <= 0). The speculative pass therefore only tracks sign changes of d; the exact
-  // replay below then decides with the reference's own rounded comparisons. The two can disagree only
-  // when |d| is within a few ulps of zero (a spike time tied with an input to the last bits).
-  float dprev[JPT];
-  bool first = true;
+  const float* wl = w + (FULL ? jbase + lane : 0);
   int k = 0;
   bool all_done = false;
-  for (; k + kChunk <= nvalid && !all_done; k += kChunk) {
-    float ws0[JPT], ys0[JPT];
-    int acc[JPT];
+  while (k < nvalid && !all_done) {
+    const int cnt = min(CH, nvalid - k);
+    float xs[CH];
+    float wv[CH][JPT];
 #pragma unroll
-    for (int m = 0; m < JPT; ++m) { ws0[m] = wsum[m]; ys0[m] = ysum[m]; acc[m] = 0; }
-    if (first) {
-      const float x0 = key_value(keys[0]);
+    for (int u = 0; u < CH; ++u) {
+      const WalkEntry e = ents[k + (u < cnt ? u : 0)];
+      xs[u] = __uint_as_float(e.x);
+      const float* wrow = wl + e.y;
 #pragma unroll
-      for (int m = 0; m < JPT; ++m) {
-        dprev[m] = fmaf(-x0, wsum[m], ysum[m]);
-        if (armed0[m]) acc[m] = -1;  // bias alone may already fire: take the first steps exactly
-      }
-      first = false;
+      for (int m = 0; m < JPT; ++m) wv[u][m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
     }
-
 #pragma unroll
-    for (int u = 0; u < kChunk; ++u) {
-      const u64 e = keys[k + u];
-      const float x = key_value(e);
-      const float* wrow = w + (size_t)(uint32_t)e * J;
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) {
-        const float wv = FULL ? __ldg(wrow + jbase + lane + 32 * m) : __ldg(wrow + jl[m]);
-        const float d = fmaf(-x, wsum[m], ysum[m]);
-        acc[m] |= __float_as_int(d) ^ __float_as_int(dprev[m]);
-        dprev[m] = d;
-        wsum[m] += wv;
-        ysum[m] = fmaf(x, wv, ysum[m]);
-      }
-    }
-
-    bool flag[JPT];
-    bool need = false;
-#pragma unroll
-    for (int m = 0; m < JPT; ++m) {
-      flag[m] = (acc[m] < 0) && live[m];
-      need |= flag[m];
-      if (!live[m]) { wsum[m] = ws0[m]; ysum[m] = ys0[m]; }  // finished outputs keep their sums
-    }
-    if (__any_sync(0xffffffffu, need)) {
-      // ---- exact replay of these eight steps for the outputs whose test tripped
-      const float xprev = k > 0 ? key_value(keys[k - 1]) : 0.f;
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) {
-        if (flag[m]) {
-          wsum[m] = ws0[m];
-          ysum[m] = ys0[m];
-          armed[m] = k > 0 ? ratio_gt(ysum[m], wsum[m], xprev) : armed0[m];
-        }
-      }
-      for (int u = 0; u < kChunk; ++u) {
-        const u64 e = keys[k + u];
-        const float x = key_value(e);
-        const float* wrow = w + (size_t)(uint32_t)e * J;
+    for (int u = 0; u < CH; ++u) {
+      if (u < cnt) {
+        const float x = xs[u];
+        int orall = 0;
 #pragma unroll
         for (int m = 0; m < JPT; ++m) {
-          if (flag[m]) {
-            const float wv = __ldg(wrow + jl[m]);
-            walk_step(x, wv, wsum[m], ysum[m], armed[m], live[m]);
+          const float d = fmaf(-x, wsum[m], ysum[m]);
+          const int wi = __float_as_int(wsum[m]);
+          const int f = ~(__float_as_int(dprev[m]) ^ wi) & (__float_as_int(d) ^ wi);
+          orall |= f & livemask[m];
+          dprev[m] = d;
+        }
+        if (__any_sync(0xffffffffu, orall < 0)) {
+#pragma unroll
+          for (int m = 0; m < JPT; ++m) {
+            if (livemask[m] && have_prev && ratio_gt(ysum[m], wsum[m], xprev) && ratio_le(ysum[m], wsum[m], x)) {
+              livemask[m] = 0;  // spike lies in (previous input, x]: freeze the sums
+              wfin[m] = wsum[m];
+              yfin[m] = ysum[m];
+            }
           }
         }
+#pragma unroll
+        for (int m = 0; m < JPT; ++m) {
+          wsum[m] += wv[u][m];
+          ysum[m] = fmaf(x, wv[u][m], ysum[m]);
+        }
+        xprev = x;
+        have_prev = true;
       }
     }
-    bool any_live = false;
+    k += cnt;
+    int any_live = 0;
 #pragma unroll
-    for (int m = 0; m < JPT; ++m) any_live |= live[m];
-    all_done = !__any_sync(0xffffffffu, any_live);
-  }
-
-  if (!all_done) {
-    // ---- tail (fewer than eight inputs left): exact steps
-    const float xprev = k > 0 ? key_value(keys[k - 1]) : 0.f;
-#pragma unroll
-    for (int m = 0; m < JPT; ++m)
-      if (live[m]) armed[m] = k > 0 ? ratio_gt(ysum[m], wsum[m], xprev) : armed0[m];
-    for (; k < nvalid; ++k) {
-      const u64 e = keys[k];
-      const float x = key_value(e);
-      const float* wrow = w + (size_t)(uint32_t)e * J;
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) {
-        const float wv = __ldg(wrow + jl[m]);
-        walk_step(x, wv, wsum[m], ysum[m], armed[m], live[m]);
-      }
-    }
+    for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
+    all_done = !__any_sync(0xffffffffu, any_live != 0);
   }
 
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
     // an output that stopped has fired; one that consumed every input fires iff it is armed
-    const bool fired = !live[m] || armed[m];
+    bool fired = true;
+    float ws = wfin[m], ys = yfin[m];
+    if (livemask[m]) {
+      ws = wsum[m]; ys = ysum[m];
+      fired = have_prev && ratio_gt(ys, ws, xprev);
+    }
     float yv = g.maxv, iv = 0.f;
     if (fired) {
-      iv = __fdividef(1.0f, wsum[m]);
-      yv = ysum[m] * iv;
+      iv = __fdividef(1.0f, ws);
+      yv = ys * iv;
       if (yv >= g.maxv) { yv = g.maxv; iv = 0.f; }
     }
     if (jok[m]) {
@@ -334,7 +299,7 @@ __device__ __forceinline__ void bitonic_sort_cta(u64* keys, int n, int tid) {
 // Sort kernel: one warp per row. Shared memory per warp: two key buffers of I entries and the four
 // digit histograms. Sorted keys go to keys_g[r*istride ..], their count to nvalid_g[r].
 __global__ void __launch_bounds__(kFwdThreads)
-snn_sort_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__ keys_g, int* __restrict__ nvalid_g,
+snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __restrict__ keys_g, int* __restrict__ nvalid_g,
                 int istride) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int I = g.I, R = g.R;
@@ -352,8 +317,11 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__
     if (n <= 32) { sort_small(a, b, n, lane); res = b; }
     else res = radix_sort_row(a, b, n, hist, lane);
     __syncwarp();
-    u64* dst = keys_g + (size_t)r * istride;
-    for (int i = lane; i < n; i += 32) dst[i] = res[i];
+    WalkEntry* dst = keys_g + (size_t)r * istride;
+    for (int i = lane; i < n; i += 32) {
+      const u64 e = res[i];
+      dst[i] = make_uint2(__float_as_uint(key_value(e)), (uint32_t)e * (uint32_t)g.J);
+    }
     if (lane == 0) nvalid_g[r] = n;
     __syncwarp();
   }
@@ -361,7 +329,7 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__
 
 // Rows too long for two buffers per warp: one row per CTA at a time, in-place bitonic network.
 __global__ void __launch_bounds__(kFwdThreads)
-snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, u64* __restrict__ keys_g,
+snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __restrict__ keys_g,
                      int* __restrict__ nvalid_g, int istride) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   u64* keys = reinterpret_cast<u64*>(smem_raw);
@@ -375,8 +343,11 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, u64* __restr
     __syncthreads();
     const int n = s_n;
     bitonic_sort_cta(keys, n, tid);
-    u64* dst = keys_g + (size_t)r * istride;
-    for (int i = tid; i < n; i += kFwdThreads) dst[i] = keys[i];
+    WalkEntry* dst = keys_g + (size_t)r * istride;
+    for (int i = tid; i < n; i += kFwdThreads) {
+      const u64 e = keys[i];
+      dst[i] = make_uint2(__float_as_uint(key_value(e)), (uint32_t)e * (uint32_t)g.J);
+    }
     if (tid == 0) nvalid_g[r] = n;
     __syncthreads();
   }
@@ -385,7 +356,7 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, u64* __restr
 // Walk kernel: every warp takes (row, block of 32*JPT outputs) items, adjacent warps share a row.
 template <int JPT>
 __global__ void __launch_bounds__(kFwdThreads)
-snn_walk_kernel(const Geometry g, const u64* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
+snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                 const float* __restrict__ w, float* __restrict__ out) {
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
@@ -397,12 +368,12 @@ snn_walk_kernel(const Geometry g, const u64* __restrict__ keys_g, const int* __r
   const long wstride = (long)gridDim.x * kFwdWarps;
   for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
     const int r = (int)(item / jchunks), jc = (int)(item - (long)r * jchunks);
-    const u64* krow = keys_g + (size_t)r * istride;
+    const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __ldg(nvalid_g + r);
     if (full_j)
-      walk_row<JPT, true>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), true>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
     else
-      walk_row<JPT, false>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), false>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
   }
 }
 
@@ -411,7 +382,7 @@ int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of k
 size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
 
 template <int JPT>
-int launch_walk(const Geometry& g, const u64* keys_g, const int* nvalid_g, const float* w, float* out,
+int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
                 const LaunchInfo& li, cudaStream_t s) {
   const int jchunks = (g.J + 32 * JPT - 1) / (32 * JPT);
   const long items = (long)g.R * jchunks;
@@ -432,7 +403,7 @@ size_t forward_workspace_bytes(const Geometry& g) {
 int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void* ws, size_t ws_bytes,
                    const LaunchInfo& li, cudaStream_t s) {
   if (!ws || ws_bytes < forward_workspace_bytes(g)) return -5;
-  u64* keys_g = static_cast<u64*>(ws);
+  WalkEntry* keys_g = static_cast<WalkEntry*>(ws);
   int* nvalid_g = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + keys_bytes(g));
   const int istride = key_stride(g);
 
