@@ -25,19 +25,23 @@ constexpr int kJTP = kJT + 4;   // padded row stride: keeps float4 alignment, sp
 constexpr int kRT = 16;         // reduction chunk of the dW kernel (rows r per shared-memory tile)
 
 // ------------------------------------------------------------------------------------------- dX
-// "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C).
+// "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C). The
+// reduction runs over tiles t = (tap, block of 16 outputs); the loads of tile t+1 are issued before
+// the arithmetic of tile t and parked in registers, shared memory is double buffered.
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
               const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
-  __shared__ __align__(16) float Ys[kTile * kJTP];
-  __shared__ __align__(16) float Us[kTile * kJTP];
-  __shared__ __align__(16) float Ws[kTile * kJTP];
-  __shared__ int s_orow[kTile];
+  __shared__ __align__(16) float Ys[2][kTile * kJTP];
+  __shared__ __align__(16) float Us[2][kTile * kJTP];
+  __shared__ __align__(16) float Ws[2][kTile * kJTP];
+  __shared__ int s_pb[kTile], s_ph[kTile], s_pw[kTile];
 
   const int J = g.J;
   const int CH = g.is_conv ? g.C : g.I;
   const int P = g.is_conv ? g.B * g.H * g.W : g.R;
   const int taps = g.is_conv ? g.Kh * g.Kw : 1;
+  const int njt = (J + kJT - 1) / kJT;
+  const int ntiles = taps * njt;
   const float maxcomp = g.maxv - 0.1f;
   const float* __restrict__ yv = out;
   const float* __restrict__ iv = out + (size_t)g.R * J;
@@ -45,6 +49,23 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
   const int tid = threadIdx.x;
   const int tr = tid >> 4, ti = tid & 15;
   const int p0 = blockIdx.x * kTile, c0 = blockIdx.y * kTile;
+
+  if (tid < kTile) {
+    const int p = p0 + tid;
+    int pb = -1, ph = 0, pw = 0;
+    if (p < P) {
+      if (!g.is_conv) {
+        pb = p;
+      } else {
+        const int ww = p % g.W;
+        const int t = p / g.W;
+        pb = t / g.H;
+        ph = t % g.H + g.pad_top;
+        pw = ww + g.pad_left;
+      }
+    }
+    s_pb[tid] = pb; s_ph[tid] = ph; s_pw[tid] = pw;
+  }
 
   float xr[4][4], acc[4][4];
 #pragma unroll
@@ -55,77 +76,95 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
       xr[a][b] = (p < P && c < CH) ? __ldg(x + (size_t)p * CH + c) : CUDART_INF_F;
       acc[a][b] = 0.f;
     }
+  __syncthreads();
 
   const int ld_jj = tid & 15, ld_row = tid >> 4;  // tile loaders: 16 consecutive j per row
+  float py[4], pu[4], pwv[4];                     // the next tile, parked in registers
 
-  for (int tap = 0; tap < taps; ++tap) {
-    // which output row (receptive field) does each point of the tile feed through this tap?
-    if (tid < kTile) {
-      const int p = p0 + tid;
-      int orow = -1;
-      if (p < P) {
-        if (!g.is_conv) {
-          orow = p;
-        } else {
-          const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
-          const int ww = p % g.W;
-          const int t = p / g.W;
-          const int h = t % g.H;
-          const int b = t / g.H;
-          const int hh = h + g.pad_top - kh, wq = ww + g.pad_left - kw;
-          if (hh >= 0 && wq >= 0 && hh % g.Sh == 0 && wq % g.Sw == 0) {
-            const int nh = hh / g.Sh, nw = wq / g.Sw;
-            if (nh < g.Nh && nw < g.Nw) orow = (b * g.Nh + nh) * g.Nw + nw;
-          }
+  auto fetch = [&](int t) {
+    const int tap = t / njt;
+    const int j = (t - tap * njt) * kJT + ld_jj;
+    int kh = 0, kw = 0;
+    if (g.is_conv) { kh = tap / g.Kw; kw = tap - kh * g.Kw; }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int row = ld_row + 16 * q;
+      int orow = s_pb[row];
+      if (g.is_conv && orow >= 0) {
+        const int hh = s_ph[row] - kh, wq = s_pw[row] - kw;
+        int nh = hh, nw = wq;
+        bool ok = hh >= 0 && wq >= 0;
+        if (g.Sh != 1 || g.Sw != 1) {
+          nh = hh / g.Sh; nw = wq / g.Sw;
+          ok = ok && nh * g.Sh == hh && nw * g.Sw == wq;
         }
+        ok = ok && nh < g.Nh && nw < g.Nw;
+        orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
       }
-      s_orow[tid] = orow;
+      float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
+      if (orow >= 0 && j < J) {
+        const size_t o = (size_t)orow * J + j;
+        y = __ldg(yv + o);
+        u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
+      }
+      const int c = c0 + row;
+      if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
+      py[q] = y; pu[q] = u; pwv[q] = wv;
     }
+  };
+  auto park = [&](int buf) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int row = ld_row + 16 * q;
+      Ys[buf][row * kJTP + ld_jj] = py[q];
+      Us[buf][row * kJTP + ld_jj] = pu[q];
+      Ws[buf][row * kJTP + ld_jj] = pwv[q];
+    }
+  };
+
+  fetch(0);
+  park(0);
+  __syncthreads();
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) fetch(t + 1);
+
+#pragma unroll
+    for (int j4 = 0; j4 < kJT; j4 += 4) {
+      float4 y4[4], u4[4], w4[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        y4[a] = *reinterpret_cast<const float4*>(&Ys[buf][(tr + 16 * a) * kJTP + j4]);
+        u4[a] = *reinterpret_cast<const float4*>(&Us[buf][(tr + 16 * a) * kJTP + j4]);
+      }
+#pragma unroll
+      for (int b = 0; b < 4; ++b) w4[b] = *reinterpret_cast<const float4*>(&Ws[buf][(ti + 16 * b) * kJTP + j4]);
+      // one output column at a time across all 16 accumulators: no back-to-back dependent FMAs
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (xr[a][b] <= y4[a].x) acc[a][b] = fmaf(u4[a].x, w4[b].x, acc[a][b]);
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (xr[a][b] <= y4[a].y) acc[a][b] = fmaf(u4[a].y, w4[b].y, acc[a][b]);
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (xr[a][b] <= y4[a].z) acc[a][b] = fmaf(u4[a].z, w4[b].z, acc[a][b]);
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (xr[a][b] <= y4[a].w) acc[a][b] = fmaf(u4[a].w, w4[b].w, acc[a][b]);
+    }
+
+    if (t + 1 < ntiles) park(buf ^ 1);
     __syncthreads();
-
-    for (int j0 = 0; j0 < J; j0 += kJT) {
-      const int j = j0 + ld_jj;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const int row = ld_row + 16 * q;
-        const int orow = s_orow[row];
-        float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
-        if (orow >= 0 && j < J) {
-          const size_t o = (size_t)orow * J + j;
-          y = __ldg(yv + o);
-          u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
-        }
-        const int c = c0 + row;
-        if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
-        Ys[row * kJTP + ld_jj] = y;
-        Us[row * kJTP + ld_jj] = u;
-        Ws[row * kJTP + ld_jj] = wv;
-      }
-      __syncthreads();
-
-#pragma unroll
-      for (int j4 = 0; j4 < kJT; j4 += 4) {
-        float4 y4[4], u4[4], w4[4];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-          y4[a] = *reinterpret_cast<const float4*>(&Ys[(tr + 16 * a) * kJTP + j4]);
-          u4[a] = *reinterpret_cast<const float4*>(&Us[(tr + 16 * a) * kJTP + j4]);
-        }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) w4[b] = *reinterpret_cast<const float4*>(&Ws[(ti + 16 * b) * kJTP + j4]);
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            const float xv = xr[a][b];
-            if (xv <= y4[a].x) acc[a][b] = fmaf(u4[a].x, w4[b].x, acc[a][b]);
-            if (xv <= y4[a].y) acc[a][b] = fmaf(u4[a].y, w4[b].y, acc[a][b]);
-            if (xv <= y4[a].z) acc[a][b] = fmaf(u4[a].z, w4[b].z, acc[a][b]);
-            if (xv <= y4[a].w) acc[a][b] = fmaf(u4[a].w, w4[b].w, acc[a][b]);
-          }
-      }
-      __syncthreads();
-    }
   }
 
 #pragma unroll
@@ -140,13 +179,14 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
 // ------------------------------------------------------------------------------------------- dW
 // Output tile 64 (fan-in rows i, bias row included) x 64 (outputs j); blockIdx.z selects a slice of
 // the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane of the workspace.
+// Same software pipeline as dX: the next 16 rows are loaded into registers while the current 16 are
+// being reduced out of (double-buffered) shared memory.
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
-  __shared__ __align__(16) float Xs[kRT * kTile];
-  __shared__ __align__(16) float Ys[kRT * kTile];
-  __shared__ __align__(16) float Us[kRT * kTile];
-  __shared__ int s_b[kRT], s_h0[kRT], s_w0[kRT];
+  __shared__ __align__(16) float Xs[2][kRT * kTile];
+  __shared__ __align__(16) float Ys[2][kRT * kTile];
+  __shared__ __align__(16) float Us[2][kRT * kTile];
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
@@ -171,31 +211,25 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     l_kh = tap / g.Kw;
     l_kw = tap - l_kh * g.Kw;
   }
+  // position of this loader's first row (r_begin + ld_r) in the output grid, advanced incrementally
+  int c_b = 0, c_nh = 0, c_nw = 0;
+  if (g.is_conv) {
+    const int r = r_begin + ld_r;
+    c_nw = r % g.Nw;
+    const int t = r / g.Nw;
+    c_nh = t % g.Nh;
+    c_b = t / g.Nh;
+  }
+  auto advance = [&](int by) {  // move (c_b, c_nh, c_nw) forward by `by` rows
+    c_nw += by;
+    while (c_nw >= g.Nw) { c_nw -= g.Nw; if (++c_nh == g.Nh) { c_nh = 0; ++c_b; } }
+  };
 
-  float acc[4][4];
-#pragma unroll
-  for (int a = 0; a < 4; ++a)
-#pragma unroll
-    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-
-  for (int rb = r_begin; rb < r_end; rb += kRT) {
-    if (g.is_conv && tid < kRT) {
-      const int r = rb + tid;
-      if (r < r_end) {
-        const int nw = r % g.Nw;
-        const int t = r / g.Nw;
-        const int nh = t % g.Nh;
-        s_b[tid] = t / g.Nh;
-        s_h0[tid] = nh * g.Sh - g.pad_top;
-        s_w0[tid] = nw * g.Sw - g.pad_left;
-      }
-    }
-    if (g.is_conv) __syncthreads();
-
+  float px[kRT / 4], py[kRT / 4], pu[kRT / 4];
+  auto fetch = [&](int rb) {
 #pragma unroll
     for (int q = 0; q < kRT / 4; ++q) {
-      const int rr = ld_r + 4 * q;
-      const int r = rb + rr;
+      const int r = rb + ld_r + 4 * q;
       // padding of the tile: x=+inf, y=0, u=0 gives min(x,y)-y = 0 and a zero product (never inf-inf)
       float xv = CUDART_INF_F, y = 0.f, u = 0.f;
       if (r < r_end) {
@@ -203,9 +237,9 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
           if (!g.is_conv) {
             xv = __ldg(x + (size_t)r * I + li);
           } else {
-            const int h = s_h0[rr] + l_kh, ww = s_w0[rr] + l_kw;
+            const int h = c_nh * g.Sh - g.pad_top + l_kh, ww = c_nw * g.Sw - g.pad_left + l_kw;
             if (h >= 0 && h < g.H && ww >= 0 && ww < g.W)
-              xv = __ldg(x + (((size_t)s_b[rr] * g.H + h) * g.W + ww) * g.C + l_c);
+              xv = __ldg(x + (((size_t)c_b * g.H + h) * g.W + ww) * g.C + l_c);
           }
         } else if (li == I && g.has_bias) {
           xv = g.biasvolt;
@@ -216,17 +250,43 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
           u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
         }
       }
-      Xs[rr * kTile + ld_c] = xv;
-      Ys[rr * kTile + ld_c] = y;
-      Us[rr * kTile + ld_c] = u;
+      px[q] = xv; py[q] = y; pu[q] = u;
+      if (g.is_conv) advance(4);
     }
-    __syncthreads();
+  };
+  auto park = [&](int buf) {
+#pragma unroll
+    for (int q = 0; q < kRT / 4; ++q) {
+      const int rr = ld_r + 4 * q;
+      Xs[buf][rr * kTile + ld_c] = px[q];
+      Ys[buf][rr * kTile + ld_c] = py[q];
+      Us[buf][rr * kTile + ld_c] = pu[q];
+    }
+  };
+
+  float acc[4][4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+
+  if (r_begin < r_end) {
+    fetch(r_begin);
+    park(0);
+  }
+  __syncthreads();
+
+  int it = 0;
+  for (int rb = r_begin; rb < r_end; rb += kRT, ++it) {
+    const int buf = it & 1;
+    const bool more = rb + kRT < r_end;
+    if (more) fetch(rb + kRT);
 
 #pragma unroll
     for (int rr = 0; rr < kRT; ++rr) {
-      const float4 x4 = *reinterpret_cast<const float4*>(&Xs[rr * kTile + 4 * ti]);
-      const float4 y4 = *reinterpret_cast<const float4*>(&Ys[rr * kTile + 4 * tj]);
-      const float4 u4 = *reinterpret_cast<const float4*>(&Us[rr * kTile + 4 * tj]);
+      const float4 x4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTile + 4 * ti]);
+      const float4 y4 = *reinterpret_cast<const float4*>(&Ys[buf][rr * kTile + 4 * tj]);
+      const float4 u4 = *reinterpret_cast<const float4*>(&Us[buf][rr * kTile + 4 * tj]);
       const float xa[4] = {x4.x, x4.y, x4.z, x4.w};
       const float ya[4] = {y4.x, y4.y, y4.z, y4.w};
       const float ua[4] = {u4.x, u4.y, u4.z, u4.w};
@@ -239,6 +299,8 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
           acc[a][b] = fmaf(d, ua[b], acc[a][b]);
         }
     }
+
+    if (more) park(buf ^ 1);
     __syncthreads();
   }
 

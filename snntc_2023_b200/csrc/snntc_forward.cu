@@ -86,57 +86,66 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   bool have_prev = g.has_bias != 0;
 
   const float* wl = w + (FULL ? jbase + lane : 0);
+
+  // one step for all JPT outputs of this lane: pattern test, (rarely) exact test, then consume
+  auto step = [&](const float x, const float (&wv)[JPT]) {
+    int orall = 0;
+#pragma unroll
+    for (int m = 0; m < JPT; ++m) {
+      const float d = fmaf(-x, wsum[m], ysum[m]);
+      const int wi = __float_as_int(wsum[m]);
+      const int f = ~(__float_as_int(dprev[m]) ^ wi) & (__float_as_int(d) ^ wi);
+      orall |= f & livemask[m];
+      dprev[m] = d;
+    }
+    if (__any_sync(0xffffffffu, orall < 0)) {
+#pragma unroll
+      for (int m = 0; m < JPT; ++m) {
+        if (livemask[m] && have_prev && ratio_gt(ysum[m], wsum[m], xprev) && ratio_le(ysum[m], wsum[m], x)) {
+          livemask[m] = 0;  // spike lies in (previous input, x]: freeze the sums
+          wfin[m] = wsum[m];
+          yfin[m] = ysum[m];
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < JPT; ++m) {
+      wsum[m] += wv[m];
+      ysum[m] = fmaf(x, wv[m], ysum[m]);
+    }
+    xprev = x;
+    have_prev = true;
+  };
+
   int k = 0;
   bool all_done = false;
-  while (k < nvalid && !all_done) {
-    const int cnt = min(CH, nvalid - k);
+  for (; k + CH <= nvalid && !all_done; k += CH) {
     float xs[CH];
     float wv[CH][JPT];
 #pragma unroll
     for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = ents[k + (u < cnt ? u : 0)];
+      const WalkEntry e = ents[k + u];
       xs[u] = __uint_as_float(e.x);
       const float* wrow = wl + e.y;
 #pragma unroll
       for (int m = 0; m < JPT; ++m) wv[u][m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
     }
 #pragma unroll
-    for (int u = 0; u < CH; ++u) {
-      if (u < cnt) {
-        const float x = xs[u];
-        int orall = 0;
-#pragma unroll
-        for (int m = 0; m < JPT; ++m) {
-          const float d = fmaf(-x, wsum[m], ysum[m]);
-          const int wi = __float_as_int(wsum[m]);
-          const int f = ~(__float_as_int(dprev[m]) ^ wi) & (__float_as_int(d) ^ wi);
-          orall |= f & livemask[m];
-          dprev[m] = d;
-        }
-        if (__any_sync(0xffffffffu, orall < 0)) {
-#pragma unroll
-          for (int m = 0; m < JPT; ++m) {
-            if (livemask[m] && have_prev && ratio_gt(ysum[m], wsum[m], xprev) && ratio_le(ysum[m], wsum[m], x)) {
-              livemask[m] = 0;  // spike lies in (previous input, x]: freeze the sums
-              wfin[m] = wsum[m];
-              yfin[m] = ysum[m];
-            }
-          }
-        }
-#pragma unroll
-        for (int m = 0; m < JPT; ++m) {
-          wsum[m] += wv[u][m];
-          ysum[m] = fmaf(x, wv[u][m], ysum[m]);
-        }
-        xprev = x;
-        have_prev = true;
-      }
-    }
-    k += cnt;
+    for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
     int any_live = 0;
 #pragma unroll
     for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
     all_done = !__any_sync(0xffffffffu, any_live != 0);
+  }
+  if (!all_done) {
+    for (; k < nvalid; ++k) {
+      const WalkEntry e = ents[k];
+      const float* wrow = wl + e.y;
+      float wv[JPT];
+#pragma unroll
+      for (int m = 0; m < JPT; ++m) wv[m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
+      step(__uint_as_float(e.x), wv);
+    }
   }
 
 #pragma unroll
