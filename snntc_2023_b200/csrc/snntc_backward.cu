@@ -79,7 +79,8 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
   __syncthreads();
 
   const int ld_jj = tid & 15, ld_row = tid >> 4;  // tile loaders: 16 consecutive j per row
-  float py[4], pu[4], pwv[4];                     // the next tile, parked in registers
+  float py[4], pg[4], pi[4], pwv[4];              // the next tile, parked RAW in registers: nothing
+                                                  // may touch the loaded values before the arithmetic below
 
   auto fetch = [&](int t) {
     const int tap = t / njt;
@@ -101,15 +102,16 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
         ok = ok && nh < g.Nh && nw < g.Nw;
         orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
       }
-      float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
+      float y = -CUDART_INF_F, gv = 0.f, iq = 0.f, wv = 0.f;
       if (orow >= 0 && j < J) {
         const size_t o = (size_t)orow * J + j;
         y = __ldg(yv + o);
-        u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
+        gv = __ldg(grad + o);
+        iq = __ldg(iv + o);
       }
       const int c = c0 + row;
       if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
-      py[q] = y; pu[q] = u; pwv[q] = wv;
+      py[q] = y; pg[q] = gv; pi[q] = iq; pwv[q] = wv;
     }
   };
   auto park = [&](int buf) {
@@ -117,7 +119,7 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     for (int q = 0; q < 4; ++q) {
       const int row = ld_row + 16 * q;
       Ys[buf][row * kJTP + ld_jj] = py[q];
-      Us[buf][row * kJTP + ld_jj] = pu[q];
+      Us[buf][row * kJTP + ld_jj] = (py[q] > maxcomp) ? 0.f : pg[q] * pi[q];
       Ws[buf][row * kJTP + ld_jj] = pwv[q];
     }
   };
@@ -225,13 +227,13 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     while (c_nw >= g.Nw) { c_nw -= g.Nw; if (++c_nh == g.Nh) { c_nh = 0; ++c_b; } }
   };
 
-  float px[kRT / 4], py[kRT / 4], pu[kRT / 4];
+  float px[kRT / 4], py[kRT / 4], pg[kRT / 4], pi[kRT / 4];  // parked raw, see dX
   auto fetch = [&](int rb) {
 #pragma unroll
     for (int q = 0; q < kRT / 4; ++q) {
       const int r = rb + ld_r + 4 * q;
       // padding of the tile: x=+inf, y=0, u=0 gives min(x,y)-y = 0 and a zero product (never inf-inf)
-      float xv = CUDART_INF_F, y = 0.f, u = 0.f;
+      float xv = CUDART_INF_F, y = 0.f, gv = 0.f, iq = 0.f;
       if (r < r_end) {
         if (li < I) {
           if (!g.is_conv) {
@@ -247,10 +249,11 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
         if (lj < J) {
           const size_t o = (size_t)r * J + lj;
           y = __ldg(yv + o);
-          u = (y > maxcomp) ? 0.f : __ldg(grad + o) * __ldg(iv + o);
+          gv = __ldg(grad + o);
+          iq = __ldg(iv + o);
         }
       }
-      px[q] = xv; py[q] = y; pu[q] = u;
+      px[q] = xv; py[q] = y; pg[q] = gv; pi[q] = iq;
       if (g.is_conv) advance(4);
     }
   };
@@ -260,7 +263,7 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
       const int rr = ld_r + 4 * q;
       Xs[buf][rr * kTile + ld_c] = px[q];
       Ys[buf][rr * kTile + ld_c] = py[q];
-      Us[buf][rr * kTile + ld_c] = pu[q];
+      Us[buf][rr * kTile + ld_c] = (py[q] > maxcomp) ? 0.f : pg[q] * pi[q];
     }
   };
 
