@@ -116,6 +116,31 @@ SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx,
                                      void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * SnnFcGrad without a caller workspace. This entry point has no counterpart in the reference.
+ *
+ * For callers that have no way to allocate device memory when the dense backward runs (an operator
+ * plugin that is handed only its declared inputs and outputs, a loop with a fixed memory plan, a
+ * process whose device memory belongs to another pool): same arguments and results as
+ * snntc_fc_backward, minus the workspace. The partial weight-gradient tiles go to a fixed array of
+ * SNNTC_NOALLOC_SCRATCH_BYTES that is part of the library image, so every GPU that loads the library
+ * holds that much memory until the process exits. The call allocates and frees nothing.
+ *   - Problems whose partial tiles need more than the array (snntc_fc_backward_workspace_bytes() >
+ *     snntc_noalloc_scratch_bytes()) are refused with SNNTC_E_WORKSPACE; nothing is launched.
+ *   - The first call on each device resolves the array's device address and reads two device
+ *     attributes; make that first call outside any stream capture, with the device current.
+ *   - All calls on a device share the one array. Calls whose kernels can overlap on the GPU (two
+ *     streams, two host threads) race on it: run them one after the other on one stream, or order
+ *     the streams with events. The array keeps the previous call's contents; the kernels overwrite
+ *     every element they later read, so no clearing is needed between calls.
+ */
+#define SNNTC_NOALLOC_SCRATCH_BYTES (8u << 20)
+SNNTC_API size_t snntc_noalloc_scratch_bytes(void);
+SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, const float* w,
+                                        const float* params6_host, const float* out_2BJ,
+                                        float* dx, float* dw, float* dparams6,
+                                        int B, int I, int w_rows, int J, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Measurement helpers (no counterpart in the reference).
  *   snntc_launch_count            kernels launched by this library since it was loaded
  *   snntc_profile_backward_parts  bit 0: run the dX kernel, bit 1: run the dW kernels (default 3);
