@@ -254,9 +254,8 @@ class NetWorkload:
         loss = self.net.loss(z, lab)
         loss.backward()
         if self.world > 1:
-            import torch.distributed as dist
-            dist.all_reduce(self.net.flat_grad)
-            self.net.flat_grad.mul_(1.0 / self.world)
+            from snntc_2023_b200 import ddp
+            ddp.allreduce_mean_(self.net.flat_grad, self.world)
         if self.optimize:
             self.opt.step()
         return loss

@@ -1,0 +1,129 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header declares, argument
+validation answers with the documented status codes before anything touches a device, and the
+Python layer keeps the reference's surface (SNN_TC_Modules.py:42-43,103-105,48-49,121-123)."""
+import ctypes
+import math
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "snntc_b200.h")).read()
+    return sorted(set(re.findall(r"SNNTC_API[^;(]*?\b(snntc_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from snntc_2023_b200 import _lib
+    lib = _lib.load()
+    names = _declared_symbols()
+    assert len(names) >= 17
+    for n in names:
+        assert hasattr(lib, n), "libsnntc_b200.so does not export %s" % n
+    assert set(names) == set(_lib.SYMBOLS), "ctypes table and header disagree: %s" % (set(names) ^ set(_lib.SYMBOLS))
+    assert lib.snntc_version().startswith(b"snntc_b200")
+    assert lib.snntc_status_string(0) == b"ok"
+
+
+def test_validation_status_codes_without_a_device():
+    from snntc_2023_b200 import _lib
+    lib = _lib.load()
+    p6 = np.array([1e5, 1e-10, 1.0, 0, 0, 1.0], np.float32)
+    P = p6.ctypes.data
+    fake = 0x1000  # never dereferenced: every call below is rejected during validation
+    fwd = lib.snntc_fc_forward
+    assert fwd(0, fake, P, fake, 4, 8, 9, 3, 0, 0, 0) == -1                 # null input
+    assert fwd(fake, fake, 0, fake, 4, 8, 9, 3, 0, 0, 0) == -1              # null params
+    assert fwd(fake, fake, P, fake, 0, 8, 9, 3, 0, 0, 0) == -2              # empty batch
+    assert fwd(fake, fake, P, fake, 4, 8, 8, 3, 0, 0, 0) == -3              # bias on, but no bias row
+    assert fwd(fake, fake, P, fake, 4, 8, 10, 3, 0, 0, 0) == -3
+    assert fwd(fake, fake, P, fake, 70000, 40000, 40001, 3, 0, 0, 0) == -4  # B*I > 2^31-1
+    p6[0] = 0.5
+    assert fwd(fake, fake, P, fake, 4, 8, 9, 3, 0, 0, 0) == -8              # MAX_SPIKE_TIME must exceed 1
+    p12 = np.array([1e5, 0, 0, 1e-10, 1.0, 0, 3, 3, 1, 1, 1, 0.0], np.float32)
+    cv = lib.snntc_cv_forward
+    assert cv(fake, fake, p12.ctypes.data, fake, 2, 8, 8, 4, 37, 5, 1, 1, 8, 8, 0, 0, 0) == -3   # 3*3*4 = 36 rows expected
+    assert cv(fake, fake, p12.ctypes.data, fake, 2, 8, 8, 4, 36, 5, 3, 1, 8, 8, 0, 0, 0) == -2   # pad >= kernel
+    p12[6] = 0
+    assert cv(fake, fake, p12.ctypes.data, fake, 2, 8, 8, 4, 36, 5, 1, 1, 8, 8, 0, 0, 0) == -8   # Kh = 0
+    for code in range(0, -9, -1):
+        assert len(lib.snntc_status_string(code)) > 1
+    assert lib.snntc_fc_forward_workspace_bytes(256, 784, 400) >= 256 * 784 * 8
+    assert lib.snntc_fc_backward_workspace_bytes(1, 25088, 25089, 1024) == 0   # enough tiles: no row split
+
+
+def test_no_cpu_fallback():
+    import torch
+    from snntc_2023_b200 import ops, _lib
+    x = torch.ones(2, 3); w = torch.ones(4, 5)
+    with pytest.raises(_lib.SnntcError):
+        ops.snn_fc(x, w, np.array([1e5, 1e-10, 1.0, 0, 0, 1.0], np.float32))
+    with pytest.raises(ValueError):
+        ops.snn_fc(x.double(), w, np.zeros(6, np.float32)) if False else ops._params(np.zeros(5), 6)
+
+
+def test_layer_surface_matches_reference():
+    import torch
+    import SNN_TC_Modules as SNN
+    d = SNN.SNN_dense(784, 400)
+    assert tuple(d.weight.shape) == (785, 400) and d.in_size == 785 and d.out_size == 400
+    assert np.allclose(d.Params, [1e5, 1e-10, 1.0, 0, 0, 1.0]) and d.Params.dtype == np.float32
+    assert float(d.weight[-1].abs().sum()) == 0.0            # zero bias row, stored last
+    d0 = SNN.SNN_dense(10, 4, biasvolt=0)
+    assert tuple(d0.weight.shape) == (10, 4) and d0.in_size == 10
+    wgt = np.arange(44, dtype=np.float64).reshape(11, 4)
+    d1 = SNN.SNN_dense(10, 4, weight=wgt)
+    assert d1.weight.dtype == torch.float32 and np.allclose(d1.weight.detach().numpy(), wgt)
+    with pytest.raises(ValueError):
+        SNN.SNN_dense(10, 4, weight=np.zeros((10, 4)))      # bias on by default: 11 rows expected
+    c = SNN.SNN_conv(3, 8, kernel_sizes=[3, 2], strides=2, padding='same', rates=1)
+    assert (c.Kh, c.Kw, c.Sh, c.Sw, c.C, c.Kc, c.padding) == (3, 2, 2, 2, 3, 8, 'SAME')
+    assert tuple(c.weight.shape) == (3 * 2 * 3 + 1, 8) and c.in_size == 19
+    assert np.allclose(c.Params, [1e5, 0, 0, 1e-10, 1.0, 0, 3, 2, 2, 2, 1, 1.0])
+    assert float(d.w_sum_cost()) >= 0 and float(c.l2_cost()) >= 0
+    assert callable(d.call) and callable(c.call)
+    for name in ("snnfc", "snnfc_grad", "snncv", "snncv_grad", "SNN_maxpool2d", "SNN_avgpool2d", "SNN_LRN",
+                 "loss_func", "init_weight"):
+        assert hasattr(SNN, name)
+    w = SNN.init_weight(100, 7, 1.0)
+    assert w.shape == (101, 7) and w.dtype == np.float32 and not w[-1].any()
+    # loss: softmax cross-entropy on the negated spike values
+    logit = torch.tensor([[1.0, 2.0, 0.5]]); label = torch.tensor([[0.0, 0.0, 1.0]])
+    z = -logit
+    assert abs(float(SNN.loss_func(logit, label)) - float(-(z[0, 2] - torch.logsumexp(z, 1)))) < 1e-6
+    assert abs(float(SNN.loss_func(logit, torch.tensor([2]))) - float(SNN.loss_func(logit, label))) < 1e-6
+
+
+@pytest.mark.parametrize("H,W,Kh,Kw,Sh,Sw", [(32, 32, 3, 3, 1, 1), (224, 224, 7, 7, 2, 2), (7, 9, 3, 2, 2, 1),
+                                              (10, 10, 5, 5, 2, 2), (12, 11, 6, 3, 3, 2), (5, 5, 1, 1, 1, 1), (8, 8, 3, 3, 3, 3)])
+def test_conv_geometry_matches_reference_formulas(H, W, Kh, Kw, Sh, Sw):
+    import oracle as O
+    from snntc_2023_b200 import ops
+    # SAME: total = (ceil(H/S)-1)*S + K - H, before = int(total/2)  (SNN_TC_Modules.py:147-161)
+    th = (math.ceil(H / Sh) - 1) * Sh + Kh - H
+    tw = (math.ceil(W / Sw) - 1) * Sw + Kw - W
+    pt, pl, Nh, Nw = ops.conv_geometry(H, W, Kh, Kw, Sh, Sw, "SAME")
+    assert (pt, pl) == (int(th / 2), int(tw / 2))
+    assert (Nh, Nw) == ((H + th - Kh) // Sh + 1, (W + tw - Kw) // Sw + 1) == (math.ceil(H / Sh), math.ceil(W / Sw))
+    assert (pt, pl, Nh, Nw) == O.conv_geometry(H, W, Kh, Kw, Sh, Sw, "SAME")[:4]
+    # VALID: OutDim = int((H-K)/S + 1), trailing rows/columns dropped (:163-166)
+    pt, pl, Nh, Nw = ops.conv_geometry(H, W, Kh, Kw, Sh, Sw, "VALID")
+    assert (pt, pl, Nh, Nw) == (0, 0, int((H - Kh) / Sh + 1.0), int((W - Kw) / Sw + 1.0))
+    assert (Nh - 1) * Sh + Kh <= H and (Nw - 1) * Sw + Kw <= W
+
+
+def test_network_specs_and_work_counts():
+    from snntc_2023_b200 import nets
+    rows = nets.layer_work(nets.CIFAR_CNN, (32, 32, 3))
+    assert sum(r["I"] * r["J"] for r in rows) == 3248202                      # parameters of the CIFAR-shaped net
+    assert abs(8 * sum(r["R"] * r["I"] * r["J"] for r in rows) / 1e9 - 1.2408) < 1e-3   # GFLOP per sample
+    rows = nets.layer_work(nets.IMAGENET_CNN, (224, 224, 3))
+    assert sum(r["I"] * r["J"] for r in rows) == 31372264
+    ws = nets.spec_weights(nets.MNIST_MLP, 5)
+    assert [w.shape for w in ws] == [(785, 400), (401, 400), (401, 10)] and all(not w[-1].any() for w in ws)
+    ws2 = nets.spec_weights(nets.MNIST_MLP, 5)
+    assert all(np.array_equal(a, b) for a, b in zip(ws, ws2))                 # same seed, same bytes on every rank
