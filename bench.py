@@ -238,6 +238,7 @@ class NetWorkload:
         self.h2d_bytes = batch * int(np.prod(shape)) * 4 + batch * 8
         self.d2h_bytes = 4
         self.optimize = True
+        self.collective = True   # switched off for rank-local passes (per-kernel profiling on rank 0)
 
     def stage(self, host):
         t, lab = host
@@ -253,7 +254,7 @@ class NetWorkload:
         z = torch.exp(t)
         loss = self.net.loss(z, lab)
         loss.backward()
-        if self.world > 1:
+        if self.world > 1 and self.collective:
             from snntc_2023_b200 import ddp
             ddp.allreduce_mean_(self.net.flat_grad, self.world)
         if self.optimize:
@@ -279,6 +280,7 @@ class LayerWorkload:
         self.h2d_bytes = int(np.prod(self.xshape)) * 4 + int(np.prod(self.gshape)) * 4
         self.d2h_bytes = 4
         self.optimize = False
+        self.collective = False
 
     def host_batches(self, count, seed):
         rng = np.random.default_rng(seed)
@@ -334,12 +336,13 @@ def profile_kernels(torch, wl, batches, steps, lib):
     def run(mask):
         lib.snntc_profile_backward_parts(mask)
         ops.Profile.records = []
-        opt = wl.optimize
+        opt, coll = wl.optimize, wl.collective
         wl.optimize = False
+        wl.collective = False   # this pass runs on rank 0 alone: no collective may be issued here
         for i in range(steps):
             wl.step(batches[i % len(batches)])
         torch.cuda.synchronize()
-        wl.optimize = opt
+        wl.optimize, wl.collective = opt, coll
         recs = ops.Profile.records
         ops.Profile.records = None
         lib.snntc_profile_backward_parts(3)
@@ -393,7 +396,9 @@ def run_gpu_arm(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        # a short timeout: a rank that misses a collective must end the run in minutes, not hang it
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=120))
     lib = _lib.load()
     kind, def_batch, desc = CONFIGS[args.config]
     batch = args.batch or def_batch
