@@ -4,8 +4,8 @@
 //   dX[r,i] = sum_j [x_ri <= y_rj] u_rj W[i,j]                              (snnfcgrad_kernels.cu.cc:56-65)
 //   dW[i,j] = sum_r [x_ri <= y_rj] (x_ri - y_rj) u_rj, bias row uses x=biasvolt (snnfcgrad_kernels.cu.cc:100-120)
 //
-// Both are register-tiled like an SGEMM (64x64 CTA tile, 4x4 per thread) with the predicate applied
-// per element. The same two kernels serve the convolution: dX is tiled by INPUT pixel and loops over
+// u is formed once per call by a small kernel. Both reductions are register-tiled like an SGEMM
+// (dX: 64x64 CTA tile, 4x4 per thread; dW: 128x64, 8x4 per thread) with the predicate applied per element. The same two kernels serve the convolution: dX is tiled by INPUT pixel and loops over
 // the Kh*Kw taps, gathering the covering receptive fields, so no atomics are needed (the reference
 // scatters with atomicAdd, snncvgrad_kernels.cu.cc:83); dW gathers its x tile straight from the
 // NHWC image. dW splits the row dimension over CTAs and a second kernel adds the partial tiles in a
@@ -23,13 +23,31 @@ constexpr int kTile = 64;       // CTA tile edge (rows x columns of the output)
 constexpr int kJT = 16;         // reduction chunk of the dX kernel (outputs j per shared-memory tile)
 constexpr int kJTP = kJT + 4;   // padded row stride: keeps float4 alignment, spreads rows over banks
 constexpr int kRT = 16;         // reduction chunk of the dW kernel (rows r per shared-memory tile)
+constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs, 8x4 per thread
+
+// u[r,j] = fired ? grad[r,j] * inv[r,j] : 0, once per backward call (the reference does the same with an
+// Eigen expression, snnfcgrad_kernels.cu.cc:156-173); both gradient kernels then read (y, u).
+__global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
+                             size_t n, float maxcomp) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
+    const float y = __ldg(out + e);
+    u[e] = (y > maxcomp) ? 0.f : __ldg(grad + e) * __ldg(out + n + e);
+  }
+}
+
+// acc += [x <= y] * u * w as one compare and one predicated FMA
+__device__ __forceinline__ void masked_fma(float& acc, float x, float y, float u, float w) {
+  asm("{\n\t.reg .pred p;\n\tsetp.le.f32 p, %1, %2;\n\t@p fma.rn.f32 %0, %3, %4, %0;\n\t}"
+      : "+f"(acc) : "f"(x), "f"(y), "f"(u), "f"(w));
+}
 
 // ------------------------------------------------------------------------------------------- dX
 // "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C). The
 // reduction runs over tiles t = (tap, block of 16 outputs); the loads of tile t+1 are issued before
 // the arithmetic of tile t and parked in registers, shared memory is double buffered.
 __global__ void __launch_bounds__(kBwdThreads)
-snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
+snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
   __shared__ __align__(16) float Ys[2][kTile * kJTP];
   __shared__ __align__(16) float Us[2][kTile * kJTP];
@@ -42,9 +60,7 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
   const int taps = g.is_conv ? g.Kh * g.Kw : 1;
   const int njt = (J + kJT - 1) / kJT;
   const int ntiles = taps * njt;
-  const float maxcomp = g.maxv - 0.1f;
   const float* __restrict__ yv = out;
-  const float* __restrict__ iv = out + (size_t)g.R * J;
 
   const int tid = threadIdx.x;
   const int tr = tid >> 4, ti = tid & 15;
@@ -79,8 +95,8 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
   __syncthreads();
 
   const int ld_jj = tid & 15, ld_row = tid >> 4;  // tile loaders: 16 consecutive j per row
-  float py[4], pg[4], pi[4], pwv[4];              // the next tile, parked RAW in registers: nothing
-                                                  // may touch the loaded values before the arithmetic below
+  float py[4], pu[4], pwv[4];   // the next tile, parked in registers; nothing may touch the loaded
+                                // values before the arithmetic below, or the loads stop overlapping it
 
   auto fetch = [&](int t) {
     const int tap = t / njt;
@@ -102,16 +118,15 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
         ok = ok && nh < g.Nh && nw < g.Nw;
         orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
       }
-      float y = -CUDART_INF_F, gv = 0.f, iq = 0.f, wv = 0.f;
+      float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
       if (orow >= 0 && j < J) {
         const size_t o = (size_t)orow * J + j;
         y = __ldg(yv + o);
-        gv = __ldg(grad + o);
-        iq = __ldg(iv + o);
+        u = __ldg(uv + o);
       }
       const int c = c0 + row;
       if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
-      py[q] = y; pg[q] = gv; pi[q] = iq; pwv[q] = wv;
+      py[q] = y; pu[q] = u; pwv[q] = wv;
     }
   };
   auto park = [&](int buf) {
@@ -119,7 +134,7 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     for (int q = 0; q < 4; ++q) {
       const int row = ld_row + 16 * q;
       Ys[buf][row * kJTP + ld_jj] = py[q];
-      Us[buf][row * kJTP + ld_jj] = (py[q] > maxcomp) ? 0.f : pg[q] * pi[q];
+      Us[buf][row * kJTP + ld_jj] = pu[q];
       Ws[buf][row * kJTP + ld_jj] = pwv[q];
     }
   };
@@ -146,23 +161,19 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (xr[a][b] <= y4[a].x) acc[a][b] = fmaf(u4[a].x, w4[b].x, acc[a][b]);
+        for (int b = 0; b < 4; ++b) masked_fma(acc[a][b], xr[a][b], y4[a].x, u4[a].x, w4[b].x);
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (xr[a][b] <= y4[a].y) acc[a][b] = fmaf(u4[a].y, w4[b].y, acc[a][b]);
+        for (int b = 0; b < 4; ++b) masked_fma(acc[a][b], xr[a][b], y4[a].y, u4[a].y, w4[b].y);
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (xr[a][b] <= y4[a].z) acc[a][b] = fmaf(u4[a].z, w4[b].z, acc[a][b]);
+        for (int b = 0; b < 4; ++b) masked_fma(acc[a][b], xr[a][b], y4[a].z, u4[a].z, w4[b].z);
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b)
-          if (xr[a][b] <= y4[a].w) acc[a][b] = fmaf(u4[a].w, w4[b].w, acc[a][b]);
+        for (int b = 0; b < 4; ++b) masked_fma(acc[a][b], xr[a][b], y4[a].w, u4[a].w, w4[b].w);
     }
 
     if (t + 1 < ntiles) park(buf ^ 1);
@@ -179,33 +190,32 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
 }
 
 // ------------------------------------------------------------------------------------------- dW
-// Output tile 64 (fan-in rows i, bias row included) x 64 (outputs j); blockIdx.z selects a slice of
-// the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane of the workspace.
-// Same software pipeline as dX: the next 16 rows are loaded into registers while the current 16 are
-// being reduced out of (double-buffered) shared memory.
+// Output tile 128 (fan-in rows i, bias row included) x 64 (outputs j), 8x4 per thread; blockIdx.z
+// selects a slice of the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane
+// of the workspace. Same software pipeline as dX: the next 16 rows are loaded into registers while the
+// current 16 are being reduced out of (double-buffered) shared memory.
 __global__ void __launch_bounds__(kBwdThreads)
-snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __restrict__ x,
+snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
-  __shared__ __align__(16) float Xs[2][kRT * kTile];
+  __shared__ __align__(16) float Xs[2][kRT * kTileI];
   __shared__ __align__(16) float Ys[2][kRT * kTile];
   __shared__ __align__(16) float Us[2][kRT * kTile];
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
-  const float maxcomp = g.maxv - 0.1f;
   const float* __restrict__ yv = out;
-  const float* __restrict__ iv = out + (size_t)R * J;
 
   const int tid = threadIdx.x;
   const int ti = tid >> 4, tj = tid & 15;
-  const int i0 = blockIdx.y * kTile, j0 = blockIdx.x * kTile;
+  const int i0 = blockIdx.y * kTileI, j0 = blockIdx.x * kTile;
   const int r_begin = blockIdx.z * rows_per_split;
   const int r_end = min(R, r_begin + rows_per_split);
 
-  // loader role: one fixed column of the tile, rows ld_r, ld_r+4, ...
-  const int ld_c = tid & 63, ld_r = tid >> 6;
-  const int li = i0 + ld_c;   // fan-in index this thread loads
-  const int lj = j0 + ld_c;   // output index this thread loads
+  // loader roles: x -> column (tid & 127), rows (tid >> 7) + 2q, q < 8; y/u -> column (tid & 63), rows (tid >> 6) + 4q, q < 4
+  const int lx_c = tid & (kTileI - 1), lx_r = tid >> 7;
+  const int ly_c = tid & (kTile - 1), ly_r = tid >> 6;
+  const int li = i0 + lx_c;   // fan-in index this thread loads
+  const int lj = j0 + ly_c;   // output index this thread loads
   int l_kh = 0, l_kw = 0, l_c = 0;
   if (g.is_conv && li < I) {
     const int tap = li / g.C;
@@ -213,10 +223,10 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     l_kh = tap / g.Kw;
     l_kw = tap - l_kh * g.Kw;
   }
-  // position of this loader's first row (r_begin + ld_r) in the output grid, advanced incrementally
+  // position of this loader's first x row (r_begin + lx_r) in the output grid, advanced incrementally
   int c_b = 0, c_nh = 0, c_nw = 0;
   if (g.is_conv) {
-    const int r = r_begin + ld_r;
+    const int r = r_begin + lx_r;
     c_nw = r % g.Nw;
     const int t = r / g.Nw;
     c_nh = t % g.Nh;
@@ -227,13 +237,13 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
     while (c_nw >= g.Nw) { c_nw -= g.Nw; if (++c_nh == g.Nh) { c_nh = 0; ++c_b; } }
   };
 
-  float px[kRT / 4], py[kRT / 4], pg[kRT / 4], pi[kRT / 4];  // parked raw, see dX
+  float px[kRT / 2], py[kRT / 4], pu[kRT / 4];  // parked untouched until after the arithmetic, see dX
   auto fetch = [&](int rb) {
 #pragma unroll
-    for (int q = 0; q < kRT / 4; ++q) {
-      const int r = rb + ld_r + 4 * q;
+    for (int q = 0; q < kRT / 2; ++q) {
+      const int r = rb + lx_r + 2 * q;
       // padding of the tile: x=+inf, y=0, u=0 gives min(x,y)-y = 0 and a zero product (never inf-inf)
-      float xv = CUDART_INF_F, y = 0.f, gv = 0.f, iq = 0.f;
+      float xv = CUDART_INF_F;
       if (r < r_end) {
         if (li < I) {
           if (!g.is_conv) {
@@ -246,30 +256,35 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
         } else if (li == I && g.has_bias) {
           xv = g.biasvolt;
         }
-        if (lj < J) {
-          const size_t o = (size_t)r * J + lj;
-          y = __ldg(yv + o);
-          gv = __ldg(grad + o);
-          iq = __ldg(iv + o);
-        }
       }
-      px[q] = xv; py[q] = y; pg[q] = gv; pi[q] = iq;
-      if (g.is_conv) advance(4);
+      px[q] = xv;
+      if (g.is_conv) advance(2);
+    }
+#pragma unroll
+    for (int q = 0; q < kRT / 4; ++q) {
+      const int r = rb + ly_r + 4 * q;
+      float y = 0.f, u = 0.f;
+      if (r < r_end && lj < J) {
+        const size_t o = (size_t)r * J + lj;
+        y = __ldg(yv + o);
+        u = __ldg(uv + o);
+      }
+      py[q] = y; pu[q] = u;
     }
   };
   auto park = [&](int buf) {
 #pragma unroll
+    for (int q = 0; q < kRT / 2; ++q) Xs[buf][(lx_r + 2 * q) * kTileI + lx_c] = px[q];
+#pragma unroll
     for (int q = 0; q < kRT / 4; ++q) {
-      const int rr = ld_r + 4 * q;
-      Xs[buf][rr * kTile + ld_c] = px[q];
-      Ys[buf][rr * kTile + ld_c] = py[q];
-      Us[buf][rr * kTile + ld_c] = (py[q] > maxcomp) ? 0.f : pg[q] * pi[q];
+      Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q];
+      Us[buf][(ly_r + 4 * q) * kTile + ly_c] = pu[q];
     }
   };
 
-  float acc[4][4];
+  float acc[8][4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < 8; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
 
@@ -287,14 +302,15 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
 
 #pragma unroll
     for (int rr = 0; rr < kRT; ++rr) {
-      const float4 x4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTile + 4 * ti]);
+      const float4 xa4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti]);
+      const float4 xb4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
       const float4 y4 = *reinterpret_cast<const float4*>(&Ys[buf][rr * kTile + 4 * tj]);
       const float4 u4 = *reinterpret_cast<const float4*>(&Us[buf][rr * kTile + 4 * tj]);
-      const float xa[4] = {x4.x, x4.y, x4.z, x4.w};
+      const float xa[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
       const float ya[4] = {y4.x, y4.y, y4.z, y4.w};
       const float ua[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
-      for (int a = 0; a < 4; ++a)
+      for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
           // [x<=y]*(x-y) == min(x,y)-y, bit for bit, and is 0 for sentinel inputs (x > every fired y)
@@ -309,10 +325,10 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ grad, const float* __r
 
   float* __restrict__ dst = partial + (size_t)blockIdx.z * Itot * J;
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < 8; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const int i = i0 + 4 * ti + a, j = j0 + 4 * tj + b;
+      const int i = i0 + 8 * ti + a, j = j0 + 4 * tj + b;
       if (i < Itot && j < J) dst[(size_t)i * J + j] = acc[a][b];
     }
 }
@@ -330,7 +346,7 @@ struct DwPlan { int splits; int rows_per_split; };
 
 DwPlan plan_dw(const Geometry& g, const LaunchInfo& li) {
   const int Itot = g.I + g.has_bias;
-  const long tiles = (long)((Itot + kTile - 1) / kTile) * ((g.J + kTile - 1) / kTile);
+  const long tiles = (long)((Itot + kTileI - 1) / kTileI) * ((g.J + kTile - 1) / kTile);
   long want = (3L * li.num_sms + tiles - 1) / tiles;
   long max_splits = ((long)g.R + 4 * kRT - 1) / (4 * kRT);
   if (want > max_splits) want = max_splits;
@@ -346,34 +362,43 @@ DwPlan plan_dw(const Geometry& g, const LaunchInfo& li) {
 
 }  // namespace
 
+// workspace = u[R,J] (rounded up to 256 bytes) followed by the partial dW planes (none when splits == 1)
+static size_t u_bytes(const Geometry& g) { return (((size_t)g.R * g.J * sizeof(float)) + 255) & ~(size_t)255; }
+
 size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
   const DwPlan p = plan_dw(g, li);
-  if (p.splits <= 1) return 0;
-  return (size_t)p.splits * (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
+  const size_t part = p.splits <= 1 ? 0 : (size_t)p.splits * (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
+  return u_bytes(g) + part;
 }
 
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
                     float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, cudaStream_t s) {
   const int Itot = g.I + g.has_bias;
   const int parts = backward_parts();
+  if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return -5;
+  float* uv = static_cast<float*>(ws);
+  {
+    const size_t n = (size_t)g.R * g.J;
+    size_t blocks = (n + 255) / 256;
+    if (blocks > (size_t)li.num_sms * 8) blocks = (size_t)li.num_sms * 8;
+    snn_u_kernel<<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f);
+    count_launch();
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+  }
   if (dx && (parts & 1)) {
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    snn_dx_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, w, out, dx);
+    snn_dx_kernel<<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
   if (!(parts & 2)) return OK;
   const DwPlan p = plan_dw(g, li);
   float* partial = dw;
-  if (p.splits > 1) {
-    const size_t need = (size_t)p.splits * Itot * g.J * sizeof(float);
-    if (!ws || ws_bytes < need) return -5;
-    partial = static_cast<float*>(ws);
-  }
-  dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTile - 1) / kTile, p.splits);
-  snn_dw_kernel<<<grid, kBwdThreads, 0, s>>>(g, grad, x, out, partial, p.rows_per_split);
+  if (p.splits > 1) partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g));
+  dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTileI - 1) / kTileI, p.splits);
+  snn_dw_kernel<<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (p.splits > 1) {
