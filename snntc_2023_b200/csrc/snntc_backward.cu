@@ -46,6 +46,7 @@ __device__ __forceinline__ void masked_fma(float& acc, float x, float y, float u
 // "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C). The
 // reduction runs over tiles t = (tap, block of 16 outputs); the loads of tile t+1 are issued before
 // the arithmetic of tile t and parked in registers, shared memory is double buffered.
+template <bool VEC>   // VEC: J % 4 == 0, tiles are fetched with 16-byte loads
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
@@ -94,48 +95,77 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     }
   __syncthreads();
 
-  const int ld_jj = tid & 15, ld_row = tid >> 4;  // tile loaders: 16 consecutive j per row
-  float py[4], pu[4], pwv[4];   // the next tile, parked in registers; nothing may touch the loaded
-                                // values before the arithmetic below, or the loads stop overlapping it
+  // tile loaders. Scalar form: 16 consecutive j per row, rows ld_row + 16q. Vector form: one float4 of
+  // row (tid >> 2) at columns 4*(tid & 3) for each of y, u, w. The values are parked in registers and
+  // nothing may touch them before the arithmetic below, or the loads stop overlapping it.
+  const int ld_jj = VEC ? (tid & 3) * 4 : (tid & 15);
+  const int ld_row = VEC ? (tid >> 2) : (tid >> 4);
+  float py[4], pu[4], pwv[4];
 
+  auto out_row = [&](int row, int kh, int kw) -> int {
+    int orow = s_pb[row];
+    if (g.is_conv && orow >= 0) {
+      const int hh = s_ph[row] - kh, wq = s_pw[row] - kw;
+      int nh = hh, nw = wq;
+      bool ok = hh >= 0 && wq >= 0;
+      if (g.Sh != 1 || g.Sw != 1) {
+        nh = hh / g.Sh; nw = wq / g.Sw;
+        ok = ok && nh * g.Sh == hh && nw * g.Sw == wq;
+      }
+      ok = ok && nh < g.Nh && nw < g.Nw;
+      orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
+    }
+    return orow;
+  };
   auto fetch = [&](int t) {
     const int tap = t / njt;
     const int j = (t - tap * njt) * kJT + ld_jj;
     int kh = 0, kw = 0;
     if (g.is_conv) { kh = tap / g.Kw; kw = tap - kh * g.Kw; }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int row = ld_row + 16 * q;
-      int orow = s_pb[row];
-      if (g.is_conv && orow >= 0) {
-        const int hh = s_ph[row] - kh, wq = s_pw[row] - kw;
-        int nh = hh, nw = wq;
-        bool ok = hh >= 0 && wq >= 0;
-        if (g.Sh != 1 || g.Sw != 1) {
-          nh = hh / g.Sh; nw = wq / g.Sw;
-          ok = ok && nh * g.Sh == hh && nw * g.Sw == wq;
-        }
-        ok = ok && nh < g.Nh && nw < g.Nw;
-        orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
-      }
-      float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
+    if (VEC) {
+      const int orow = out_row(ld_row, kh, kw);
+      float4 y4 = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      float4 u4 = make_float4(0.f, 0.f, 0.f, 0.f), w4 = u4;
       if (orow >= 0 && j < J) {
         const size_t o = (size_t)orow * J + j;
-        y = __ldg(yv + o);
-        u = __ldg(uv + o);
+        y4 = __ldg(reinterpret_cast<const float4*>(yv + o));
+        u4 = __ldg(reinterpret_cast<const float4*>(uv + o));
       }
-      const int c = c0 + row;
-      if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
-      py[q] = y; pu[q] = u; pwv[q] = wv;
+      const int c = c0 + ld_row;
+      if (c < CH && j < J) w4 = __ldg(reinterpret_cast<const float4*>(w + ((size_t)tap * CH + c) * J + j));
+      py[0] = y4.x; py[1] = y4.y; py[2] = y4.z; py[3] = y4.w;
+      pu[0] = u4.x; pu[1] = u4.y; pu[2] = u4.z; pu[3] = u4.w;
+      pwv[0] = w4.x; pwv[1] = w4.y; pwv[2] = w4.z; pwv[3] = w4.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int row = ld_row + 16 * q;
+        const int orow = out_row(row, kh, kw);
+        float y = -CUDART_INF_F, u = 0.f, wv = 0.f;
+        if (orow >= 0 && j < J) {
+          const size_t o = (size_t)orow * J + j;
+          y = __ldg(yv + o);
+          u = __ldg(uv + o);
+        }
+        const int c = c0 + row;
+        if (c < CH && j < J) wv = __ldg(w + ((size_t)tap * CH + c) * J + j);
+        py[q] = y; pu[q] = u; pwv[q] = wv;
+      }
     }
   };
   auto park = [&](int buf) {
+    if (VEC) {
+      *reinterpret_cast<float4*>(&Ys[buf][ld_row * kJTP + ld_jj]) = make_float4(py[0], py[1], py[2], py[3]);
+      *reinterpret_cast<float4*>(&Us[buf][ld_row * kJTP + ld_jj]) = make_float4(pu[0], pu[1], pu[2], pu[3]);
+      *reinterpret_cast<float4*>(&Ws[buf][ld_row * kJTP + ld_jj]) = make_float4(pwv[0], pwv[1], pwv[2], pwv[3]);
+    } else {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int row = ld_row + 16 * q;
-      Ys[buf][row * kJTP + ld_jj] = py[q];
-      Us[buf][row * kJTP + ld_jj] = pu[q];
-      Ws[buf][row * kJTP + ld_jj] = pwv[q];
+      for (int q = 0; q < 4; ++q) {
+        const int row = ld_row + 16 * q;
+        Ys[buf][row * kJTP + ld_jj] = py[q];
+        Us[buf][row * kJTP + ld_jj] = pu[q];
+        Ws[buf][row * kJTP + ld_jj] = pwv[q];
+      }
     }
   };
 
@@ -194,6 +224,7 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 // selects a slice of the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane
 // of the workspace. Same software pipeline as dX: the next 16 rows are loaded into registers while the
 // current 16 are being reduced out of (double-buffered) shared memory.
+template <bool VEC>   // VEC: J % 4 == 0, the y/u tiles are fetched with 16-byte loads
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
@@ -213,7 +244,8 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 
   // loader roles: x -> column (tid & 127), rows (tid >> 7) + 2q, q < 8; y/u -> column (tid & 63), rows (tid >> 6) + 4q, q < 4
   const int lx_c = tid & (kTileI - 1), lx_r = tid >> 7;
-  const int ly_c = tid & (kTile - 1), ly_r = tid >> 6;
+  const int ly_c = VEC ? (tid & 15) * 4 : (tid & (kTile - 1));
+  const int ly_r = VEC ? (tid >> 4) : (tid >> 6);
   const int li = i0 + lx_c;   // fan-in index this thread loads
   const int lj = j0 + ly_c;   // output index this thread loads
   int l_kh = 0, l_kw = 0, l_c = 0;
@@ -260,25 +292,42 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
       px[q] = xv;
       if (g.is_conv) advance(2);
     }
-#pragma unroll
-    for (int q = 0; q < kRT / 4; ++q) {
-      const int r = rb + ly_r + 4 * q;
-      float y = 0.f, u = 0.f;
+    if (VEC) {
+      const int r = rb + ly_r;
+      float4 y4 = make_float4(0.f, 0.f, 0.f, 0.f), u4 = y4;
       if (r < r_end && lj < J) {
         const size_t o = (size_t)r * J + lj;
-        y = __ldg(yv + o);
-        u = __ldg(uv + o);
+        y4 = __ldg(reinterpret_cast<const float4*>(yv + o));
+        u4 = __ldg(reinterpret_cast<const float4*>(uv + o));
       }
-      py[q] = y; pu[q] = u;
+      py[0] = y4.x; py[1] = y4.y; py[2] = y4.z; py[3] = y4.w;
+      pu[0] = u4.x; pu[1] = u4.y; pu[2] = u4.z; pu[3] = u4.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < kRT / 4; ++q) {
+        const int r = rb + ly_r + 4 * q;
+        float y = 0.f, u = 0.f;
+        if (r < r_end && lj < J) {
+          const size_t o = (size_t)r * J + lj;
+          y = __ldg(yv + o);
+          u = __ldg(uv + o);
+        }
+        py[q] = y; pu[q] = u;
+      }
     }
   };
   auto park = [&](int buf) {
 #pragma unroll
     for (int q = 0; q < kRT / 2; ++q) Xs[buf][(lx_r + 2 * q) * kTileI + lx_c] = px[q];
+    if (VEC) {
+      *reinterpret_cast<float4*>(&Ys[buf][ly_r * kTile + ly_c]) = make_float4(py[0], py[1], py[2], py[3]);
+      *reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + ly_c]) = make_float4(pu[0], pu[1], pu[2], pu[3]);
+    } else {
 #pragma unroll
-    for (int q = 0; q < kRT / 4; ++q) {
-      Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q];
-      Us[buf][(ly_r + 4 * q) * kTile + ly_c] = pu[q];
+      for (int q = 0; q < kRT / 4; ++q) {
+        Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q];
+        Us[buf][(ly_r + 4 * q) * kTile + ly_c] = pu[q];
+      }
     }
   };
 
@@ -377,6 +426,9 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   const int parts = backward_parts();
   if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return -5;
   float* uv = static_cast<float*>(ws);
+  // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
+  const bool vec = (g.J % 4 == 0) && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)uv) & 15) == 0 &&
+                   (((size_t)g.R * g.J) % 4 == 0);
   {
     const size_t n = (size_t)g.R * g.J;
     size_t blocks = (n + 255) / 256;
@@ -389,7 +441,8 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    snn_dx_kernel<<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
+    if (vec) snn_dx_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
+    else snn_dx_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
@@ -398,7 +451,8 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   float* partial = dw;
   if (p.splits > 1) partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g));
   dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTileI - 1) / kTileI, p.splits);
-  snn_dw_kernel<<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
+  if (vec) snn_dw_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
+  else snn_dw_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (p.splits > 1) {
