@@ -46,6 +46,7 @@ def parse_args():
     ap.add_argument("--cpu-sample", type=int, default=0, help="samples per CPU-baseline step (default: auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own GPU operators")
     return ap.parse_args()
 
 
@@ -384,6 +385,73 @@ def measure_fp32_peak(torch, lib):
     return best
 
 
+def time_reference_gpu(torch, wl, config, batch):
+    """Times the reference's OWN GPU operators (snn*_kernels.cu.cc compiled unmodified for sm_100a,
+    oracle/_ref/libsnntc_ref_gpu.so) on the same layer inputs as one step of the workload: per weighted
+    layer the MAX padding copy SNN_conv.call makes, the forward functor and the gradient functor (which
+    always computes dX), with their im2col/sort temporaries and per-launch device syncs. Pooling, loss
+    and optimiser are left out of this figure. Returns None when the library is not available."""
+    import oracle as O
+    if O.ref_gpu_lib() is None:
+        return None
+    from snntc_2023_b200 import SNN_TC_Modules as M
+    import torch.nn.functional as F
+    jobs = []   # (kind, x, weight, params, (Kh,Kw,Sh,Sw))
+    if hasattr(wl, "net"):
+        t, lab = wl.to_device(wl.stage(host_batches(config, batch, 1, 4242)[0]))
+        h = torch.exp(t)
+        with torch.no_grad():
+            for l in wl.net.layers:
+                if isinstance(l, M.SNN_conv):
+                    jobs.append(("conv", h, l.weight.detach(), l.Params, (l.Kh, l.Kw, l.Sh, l.Sw)))
+                elif isinstance(l, M.SNN_dense):
+                    jobs.append(("dense", h, l.weight.detach(), l.Params, None))
+                h = l(h)
+    elif config == "dense1":
+        jobs.append(("dense", torch.exp(torch.rand(wl.xshape, device="cuda")), wl.w, wl.params, None))
+    else:
+        jobs.append(("conv", torch.exp(torch.rand(wl.xshape, device="cuda")), wl.w, wl.params, (3, 3, 1, 1)))
+    need = 0
+    for kind, x, w, p, k in jobs:
+        if kind == "conv":
+            B, H, W, C = x.shape
+            rows = B * (-(-H // k[2])) * (-(-W // k[3]))
+            need = max(need, 7 * rows * k[0] * k[1] * C * 4)
+        else:
+            need = max(need, 7 * x.numel() * 4)
+    rg = O.RefGpu(min(need + (256 << 20), 40 << 30))
+    total_ms, per_layer = 0.0, []
+    for kind, x, w, p, k in jobs:
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if kind == "conv":
+            B, H, W, C = x.shape
+            pt, pl, Nh, Nw, Hp, Wp = O.conv_geometry(H, W, k[0], k[1], k[2], k[3], "SAME")
+            xp = F.pad(x, (0, 0, pl, Wp - W - pl, pt, Hp - H - pt), value=float(p[0]))
+            out = rg.cv_forward(xp, w, p)
+            g = torch.randn_like(out); g[B:] = 0
+            e0.record()   # the random upstream gradient is not part of the reference's work
+            xp = F.pad(x, (0, 0, pl, Wp - W - pl, pt, Hp - H - pt), value=float(p[0]))
+            out = rg.cv_forward(xp, w, p)
+            rg.cv_backward(g, xp, w, p, out)
+        else:
+            B = x.shape[0]
+            out = rg.fc_forward(x.contiguous(), w, p)
+            g = torch.randn_like(out); g[B:] = 0
+            e0.record()
+            out = rg.fc_forward(x.contiguous(), w, p)
+            rg.fc_backward(g, x.contiguous(), w, p, out)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        total_ms += ms
+        per_layer.append({"op": kind, "in": list(x.shape), "out": int(w.shape[1]), "ms": ms})
+    return {"ms_per_step": total_ms, "value": batch / (total_ms * 1e-3), "unit": UNIT, "layers": per_layer,
+            "what": "reference snn*_kernels.cu.cc compiled unmodified for sm_100a, forward+backward of every weighted "
+                    "layer incl. its padding copy, temporaries and device syncs; pooling/loss/optimiser excluded"}
+
+
 def run_gpu_arm(args):
     import torch
     import torch.distributed as dist
@@ -485,6 +553,14 @@ def run_gpu_arm(args):
             dt = time.perf_counter() - t0
             cpu = {"value": sample * reps / dt, "unit": UNIT, "cores": cores, "kind": ckind,
                    "sample": "%d samples per step x %d steps, batch split over %d threads" % (sample, reps, cores)}
+        ref_gpu = None
+        if world == 1 and not args.no_ref_gpu:
+            try:
+                ref_gpu = time_reference_gpu(torch, wl, args.config, batch)
+            except Exception as e:  # the reference arm must never take the bench line down with it
+                ref_gpu = {"unavailable": "%s: %s" % (type(e).__name__, e)}
+            if ref_gpu and "value" in ref_gpu:
+                ref_gpu["speedup_of_this_build"] = value / ref_gpu["value"]
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -496,6 +572,7 @@ def run_gpu_arm(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
+            "reference_gpu": ref_gpu,
         }
     if world > 1:
         dist.barrier()

@@ -244,3 +244,85 @@ def ref_cv_backward(grad2, xp, w, params12, oldout2):
                            _p(oldout2, _F), Nh, Nw, _p(dx, _F), _p(dw, _F), _p(dp, _F))
     if rc: raise ValueError("reference SnnCvGrad rejected the inputs (rc=%d)" % rc)
     return dx, dw, dp
+
+
+# ----------------------------------------------------------------------------- compiled reference GPU ops
+_ref_gpu = None
+
+
+def ref_gpu_lib():
+    """The reference's own GPU operators compiled for sm_100a, or None when not available."""
+    global _ref_gpu
+    if _ref_gpu is None:
+        path = _build.REF_GPU_SO
+        if not os.path.exists(path):
+            return None
+        _ref_gpu = ctypes.CDLL(path)
+    return _ref_gpu
+
+
+class RefGpu:
+    """Runs the reference GPU functors on torch CUDA tensors. `pool_bytes` of device scratch stand in
+    for TensorFlow's allocator (the functors materialise im2col patches, sorted copies and indices)."""
+
+    def __init__(self, pool_bytes=1 << 30):
+        import torch
+        self.torch = torch
+        self.lib = ref_gpu_lib()
+        assert self.lib is not None
+        self.pool = torch.empty(pool_bytes, dtype=torch.uint8, device="cuda")
+
+    def _args(self):
+        torch = self.torch
+        return (ctypes.c_void_p(self.pool.data_ptr()), ctypes.c_size_t(self.pool.numel()),
+                ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+
+    @staticmethod
+    def _p(t):
+        return ctypes.c_void_p(t.data_ptr())
+
+    def fc_forward(self, x, w, params6):
+        torch = self.torch
+        p = _f32(params6)
+        B, I = x.shape
+        out = torch.empty((2 * B, w.shape[1]), dtype=torch.float32, device=x.device)
+        rc = self.lib.refgpu_fc_forward(self._p(x), self._p(w), _p(p, _F), self._p(out), B, I, w.shape[0], w.shape[1],
+                                        *self._args())
+        assert rc == 0, "reference GPU SnnFc failed: CUDA error %d" % -rc
+        return out
+
+    def fc_backward(self, grad2, x, w, params6, oldout2):
+        torch = self.torch
+        p = _f32(params6)
+        B, I = x.shape
+        dx = torch.empty_like(x); dw = torch.empty_like(w); dp = torch.zeros(6, device=x.device)
+        rc = self.lib.refgpu_fc_backward(self._p(grad2), self._p(x), self._p(w), _p(p, _F), self._p(oldout2),
+                                         self._p(dx), self._p(dw), self._p(dp), B, I, w.shape[0], w.shape[1],
+                                         *self._args())
+        assert rc == 0, "reference GPU SnnFcGrad failed: CUDA error %d" % -rc
+        return dx, dw
+
+    def cv_forward(self, xp, w, params12):
+        """xp: the ALREADY padded/cropped NHWC tensor."""
+        torch = self.torch
+        p = _f32(params12)
+        B, H, W, C = xp.shape
+        Kh, Kw, Sh, Sw = (int(p[i]) for i in (6, 7, 8, 9))
+        Nh, Nw = (H - Kh) // Sh + 1, (W - Kw) // Sw + 1
+        out = torch.empty((2 * B, Nh, Nw, w.shape[1]), dtype=torch.float32, device=xp.device)
+        rc = self.lib.refgpu_cv_forward(self._p(xp), self._p(w), _p(p, _F), self._p(out), B, H, W, C, w.shape[0],
+                                        w.shape[1], Nh, Nw, *self._args())
+        assert rc == 0, "reference GPU SnnCv failed: CUDA error %d" % -rc
+        return out
+
+    def cv_backward(self, grad2, xp, w, params12, oldout2):
+        torch = self.torch
+        p = _f32(params12)
+        B, H, W, C = xp.shape
+        Nh, Nw = oldout2.shape[1], oldout2.shape[2]
+        dx = torch.empty_like(xp); dw = torch.empty_like(w); dp = torch.zeros(12, device=xp.device)
+        rc = self.lib.refgpu_cv_backward(self._p(grad2), self._p(xp), self._p(w), _p(p, _F), self._p(oldout2),
+                                         self._p(dx), self._p(dw), self._p(dp), B, H, W, C, w.shape[0], w.shape[1],
+                                         Nh, Nw, *self._args())
+        assert rc == 0, "reference GPU SnnCvGrad failed: CUDA error %d" % -rc
+        return dx, dw
