@@ -8,10 +8,32 @@
 #include <string.h>
 
 #include <atomic>
+#include <mutex>
 
 namespace snntc {
 static std::atomic<unsigned long long> g_launches{0};
 static std::atomic<int> g_backward_parts{3};
+static std::atomic<int> g_overlap{1};
+static std::mutex g_aux_mutex;
+static AuxStream g_aux[64];
+static int g_aux_state[64];   // 0 = not tried, 1 = ready, -1 = creation failed
+
+AuxStream* aux_stream() {
+  if (!g_overlap.load(std::memory_order_relaxed)) return nullptr;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_aux_mutex);
+  if (g_aux_state[dev] == 0) {
+    AuxStream& a = g_aux[dev];
+    bool ok = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) == cudaSuccess;
+    for (int i = 0; ok && i < 8; ++i) ok = cudaEventCreateWithFlags(&a.join[i], cudaEventDisableTiming) == cudaSuccess;
+    g_aux_state[dev] = ok ? 1 : -1;
+    if (!ok) cudaGetLastError();
+  }
+  return g_aux_state[dev] == 1 ? &g_aux[dev] : nullptr;
+}
+
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 int backward_parts() { return g_backward_parts.load(std::memory_order_relaxed); }
 }  // namespace snntc
@@ -152,6 +174,8 @@ const char* snntc_last_cuda_error(void) { return g_cuda_err; }
 const char* snntc_version(void) { return "snntc_b200 0.1 sm_100a"; }
 
 unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std::memory_order_relaxed); }
+
+void snntc_set_overlap(int on) { snntc::g_overlap.store(on ? 1 : 0, std::memory_order_relaxed); }
 
 void snntc_profile_backward_parts(int mask) { snntc::g_backward_parts.store(mask & 3, std::memory_order_relaxed); }
 

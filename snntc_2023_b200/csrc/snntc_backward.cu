@@ -437,14 +437,23 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
+  // dX and dW only share read-only inputs: run dX on the auxiliary stream beside dW when both are wanted
+  AuxStream* aux = (dx && parts == 3 && (long)g.R * g.J >= 65536) ? aux_stream() : nullptr;
+  cudaStream_t sdx = s;
+  if (aux) {
+    if (cudaEventRecord(aux->fork, s) != cudaSuccess || cudaStreamWaitEvent(aux->stream, aux->fork, 0) != cudaSuccess)
+      return E_CUDA;
+    sdx = aux->stream;
+  }
   if (dx && (parts & 1)) {
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    if (vec) snn_dx_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
-    else snn_dx_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, w, out, dx);
+    if (vec) snn_dx_kernel<true><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    else snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+    if (aux && cudaEventRecord(aux->join[0], aux->stream) != cudaSuccess) return E_CUDA;
   }
   if (!(parts & 2)) return OK;
   const DwPlan p = plan_dw(g, li);
@@ -463,6 +472,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
+  if (aux && cudaStreamWaitEvent(s, aux->join[0], 0) != cudaSuccess) return E_CUDA;
   return OK;
 }
 

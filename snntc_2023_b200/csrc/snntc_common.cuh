@@ -30,6 +30,19 @@ void count_launch(int n = 1);
 // profiling aid: bit 0 = run the dX kernel, bit 1 = run the dW kernels (default 3)
 int backward_parts();
 
+// One auxiliary stream and a few events per device, created on first use and kept for the life of the
+// process. Kernels of one call that do not depend on each other (the sort of the next block of rows
+// and the walk of the current one; dX and dW) are forked onto it and joined back into the caller's
+// stream with events, so the caller still sees ordinary stream order. Returns nullptr when the
+// resources cannot be created or overlap is switched off (snntc_set_overlap(0)): callers then run
+// everything on the one stream.
+struct AuxStream {
+  cudaStream_t stream;
+  cudaEvent_t fork;       // recorded on the caller's stream, waited on by the auxiliary stream
+  cudaEvent_t join[8];    // recorded on the auxiliary stream, waited on by the caller's stream
+};
+AuxStream* aux_stream();
+
 // status codes mirrored from include/snntc_b200.h
 enum { OK = 0, E_UNSUPPORTED = -6, E_CUDA = -7 };
 

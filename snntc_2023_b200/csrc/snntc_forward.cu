@@ -309,15 +309,15 @@ __device__ __forceinline__ void bitonic_sort_cta(u64* keys, int n, int tid) {
 // digit histograms. Sorted keys go to keys_g[r*istride ..], their count to nvalid_g[r].
 __global__ void __launch_bounds__(kFwdThreads)
 snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __restrict__ keys_g, int* __restrict__ nvalid_g,
-                int istride) {
+                int istride, int row_begin, int row_end) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int I = g.I, R = g.R;
+  const int I = g.I;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * (2 * (size_t)I * sizeof(u64) + kHistWords * sizeof(unsigned));
   u64* a = reinterpret_cast<u64*>(mine);
   u64* b = a + I;
   unsigned* hist = reinterpret_cast<unsigned*>(b + I);
-  for (int r = blockIdx.x * wpc + warp; r < R; r += gridDim.x * wpc) {
+  for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
     for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
     __syncwarp();
     const int n = gather_row(g, x, r, lane, a, hist);
@@ -366,17 +366,18 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* _
 template <int JPT>
 __global__ void __launch_bounds__(kFwdThreads)
 snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
-                const float* __restrict__ w, float* __restrict__ out) {
+                const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
   const int jchunks = (J + 32 * JPT - 1) / (32 * JPT);
   const bool full_j = (J % (32 * JPT)) == 0;
   float* __restrict__ y_out = out;
   float* __restrict__ inv_out = out + (size_t)R * J;
-  const long items = (long)R * jchunks;
+  const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
   for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
-    const int r = (int)(item / jchunks), jc = (int)(item - (long)r * jchunks);
+    const int rl = (int)(item / jchunks), jc = (int)(item - (long)rl * jchunks);
+    const int r = row_begin + rl;
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __ldg(nvalid_g + r);
     if (full_j)
@@ -392,13 +393,13 @@ size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * size
 
 template <int JPT>
 int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
-                const LaunchInfo& li, cudaStream_t s) {
+                const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end) {
   const int jchunks = (g.J + 32 * JPT - 1) / (32 * JPT);
-  const long items = (long)g.R * jchunks;
+  const long items = (long)(row_end - row_begin) * jchunks;
   long grid = (items + kFwdWarps - 1) / kFwdWarps;
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
-  snn_walk_kernel<JPT><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out);
+  snn_walk_kernel<JPT><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -416,38 +417,67 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   int* nvalid_g = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + keys_bytes(g));
   const int istride = key_stride(g);
 
-  // ---- sort
+  auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
+    if (g.J <= 32) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (g.J <= 64) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+  };
+
   const size_t budget = (size_t)li.max_smem_optin - 1024;
   const size_t per_warp = 2 * (size_t)g.I * sizeof(u64) + kHistWords * sizeof(unsigned);
-  if (per_warp <= budget) {
-    int wpc = (int)(budget / per_warp);
-    if (wpc > kFwdWarps) wpc = kFwdWarps;
-    // short rows: several CTAs per SM instead of one fat CTA
-    int ctas_per_sm = (int)(budget / (per_warp * wpc));
-    if (ctas_per_sm > 4) ctas_per_sm = 4;
-    if (ctas_per_sm < 1) ctas_per_sm = 1;
-    const size_t smem = per_warp * wpc;
-    if (cudaFuncSetAttribute(snn_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
-      return E_CUDA;
-    long grid = ((long)g.R + wpc - 1) / wpc;
-    const long cap = (long)li.num_sms * ctas_per_sm;
-    if (grid > cap) grid = cap;
-    snn_sort_kernel<<<(int)grid, wpc * 32, smem, s>>>(g, x, keys_g, nvalid_g, istride);
-  } else {
+  if (per_warp > budget) {
+    // rows too long for the warp sort: one CTA-wide bitonic sort per row, then the walk
     const size_t smem = (size_t)g.I * sizeof(u64);
     if (smem > budget) return E_UNSUPPORTED;
     if (cudaFuncSetAttribute(snn_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
       return E_CUDA;
     int grid = g.R < li.num_sms ? g.R : li.num_sms;
     snn_sort_long_kernel<<<grid, kFwdThreads, smem, s>>>(g, x, keys_g, nvalid_g, istride);
+    count_launch();
+    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+    return walk(s, 0, g.R);
   }
-  count_launch();
-  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
 
-  // ---- walk
-  if (g.J <= 32) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, s);
-  if (g.J <= 64) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, s);
-  return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, s);
+  int wpc = (int)(budget / per_warp);
+  if (wpc > kFwdWarps) wpc = kFwdWarps;
+  int ctas_per_sm = (int)(budget / (per_warp * wpc));   // short rows: several CTAs per SM instead of one fat CTA
+  if (ctas_per_sm > 4) ctas_per_sm = 4;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  const size_t smem = per_warp * wpc;
+  if (cudaFuncSetAttribute(snn_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
+    return E_CUDA;
+  auto sort = [&](cudaStream_t st, int r0, int r1) -> int {
+    long grid = ((long)(r1 - r0) + wpc - 1) / wpc;
+    const long cap = (long)li.num_sms * ctas_per_sm;
+    if (grid > cap) grid = cap;
+    snn_sort_kernel<<<(int)grid, wpc * 32, smem, st>>>(g, x, keys_g, nvalid_g, istride, r0, r1);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
+  };
+
+  // The sort is bound by shared-memory latency and integer work, the walk by FP32 issue and L1: run
+  // block c+1's sort beside block c's walk. Sorts go to the auxiliary stream, walks stay on the caller's.
+  AuxStream* aux = g.R >= 8 * li.num_sms ? aux_stream() : nullptr;
+  const int nblocks = aux ? 4 : 1;
+  if (!aux) {
+    int rc = sort(s, 0, g.R);
+    if (rc != OK) return rc;
+    return walk(s, 0, g.R);
+  }
+  if (cudaEventRecord(aux->fork, s) != cudaSuccess || cudaStreamWaitEvent(aux->stream, aux->fork, 0) != cudaSuccess)
+    return E_CUDA;
+  const int per = (g.R + nblocks - 1) / nblocks;
+  for (int c = 0; c < nblocks; ++c) {
+    const int r0 = c * per, r1 = r0 + per < g.R ? r0 + per : g.R;
+    if (r0 >= r1) break;
+    int rc = sort(aux->stream, r0, r1);
+    if (rc != OK) return rc;
+    if (cudaEventRecord(aux->join[c], aux->stream) != cudaSuccess || cudaStreamWaitEvent(s, aux->join[c], 0) != cudaSuccess)
+      return E_CUDA;
+    rc = walk(s, r0, r1);
+    if (rc != OK) return rc;
+  }
+  return OK;
 }
 
 }  // namespace snntc
