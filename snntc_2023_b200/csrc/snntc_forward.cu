@@ -16,6 +16,8 @@
 //      whenever the pattern shows up in any lane (see walk_row).
 #include "snntc_common.cuh"
 
+#include <math_constants.h>
+
 namespace snntc {
 
 namespace {
@@ -47,13 +49,26 @@ __device__ __forceinline__ bool ratio_le(float ysum, float wsum, float c) {
   return ya <= c * wa;
 }
 
+// sign bit set iff a has the sign of wsum and d has not: ~(a ^ wsum) & (d ^ wsum), as one LOP3
+__device__ __forceinline__ int fire_pattern(float a, float wsum, float d) {
+  int r;
+  asm("lop3.b32 %0, %1, %2, %3, 0x42;" : "=r"(r) : "r"(__float_as_int(a)), "r"(__float_as_int(wsum)), "r"(__float_as_int(d)));
+  return r;
+}
+__device__ __forceinline__ int or3(int a, int b, int c) {
+  int r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xFE;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+  return r;
+}
+
 // One warp walks one row for 32*JPT outputs (lane + 32*m). Per step and output the loop itself only
-// does the two running sums plus d = ysum - x*wsum and a sign test: a fire before consuming x means
-// "ysum/wsum > previous input" held after the previous step and "ysum/wsum <= x" holds now, which in
-// exact arithmetic is sign(wsum)*d_prev > 0 >= sign(wsum)*d. When any lane sees that pattern, the
-// warp evaluates the reference's own rounded, division-free tests for every output still running at
-// this step, so the decision is the reference's; the cheap pattern and the exact test can disagree
-// only when d is within a few ulps of zero (a spike time tied with an input to the last bits).
+// does the two running sums plus a = ysum - xprev*wsum, d = ysum - x*wsum and a sign test: a fire
+// before consuming x means "ysum/wsum > previous input" and "ysum/wsum <= x", i.e. sign(wsum)*a > 0 >=
+// sign(wsum)*d. When any lane sees that pattern, the warp evaluates the reference's own rounded,
+// division-free tests for every output still running at this step, so the decision is the
+// reference's; the cheap pattern (exact signs from two FMAs) and the reference's test (rounded
+// products) can disagree only when a or d is within an ulp of zero, i.e. when the spike time is tied
+// with an input to the last bit.
 template <int JPT, int CH, bool FULL>
 __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
@@ -61,7 +76,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   const int J = g.J;
   int jl[JPT];
   bool jok[JPT];
-  float wsum[JPT], ysum[JPT], wfin[JPT], yfin[JPT], dprev[JPT];
+  float wsum[JPT], ysum[JPT], wfin[JPT], yfin[JPT];
   int livemask[JPT];
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
@@ -70,41 +85,45 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     jl[m] = jok[m] ? j : J - 1;
     wsum[m] = -g.theta;
     ysum[m] = 0.f;
-    bool armed0 = false;
     if (g.has_bias) {  // the bias input (value biasvolt, weight row I) is always consumed first
       const float wb = __ldg(w + (size_t)g.I * J + jl[m]);
       wsum[m] += wb;
       ysum[m] = g.biasvolt * wb;
-      armed0 = ratio_gt(ysum[m], wsum[m], g.biasvolt);
     }
-    dprev[m] = armed0 ? wsum[m] : -wsum[m];  // its sign relative to wsum says "armed before the first input"
     wfin[m] = wsum[m];
     yfin[m] = ysum[m];
     livemask[m] = -1;
   }
-  float xprev = g.biasvolt;
-  bool have_prev = g.has_bias != 0;
+  // Without bias the sums start at (-theta, 0), for which "ysum/wsum > c" is false for every c >= 0, so the
+  // first step needs no special case; with bias the previous input is the bias input itself.
+  float xprev = g.has_bias ? g.biasvolt : 0.f;
 
   const float* wl = w + (FULL ? jbase + lane : 0);
 
   // one step for all JPT outputs of this lane: pattern test, (rarely) exact test, then consume
   auto step = [&](const float x, const float (&wv)[JPT]) {
-    int orall = 0;
+    int pat[JPT];
 #pragma unroll
     for (int m = 0; m < JPT; ++m) {
+      const float a = fmaf(-xprev, wsum[m], ysum[m]);
       const float d = fmaf(-x, wsum[m], ysum[m]);
-      const int wi = __float_as_int(wsum[m]);
-      const int f = ~(__float_as_int(dprev[m]) ^ wi) & (__float_as_int(d) ^ wi);
-      orall |= f & livemask[m];
-      dprev[m] = d;
+      pat[m] = fire_pattern(a, wsum[m], d);
     }
-    if (__any_sync(0xffffffffu, orall < 0)) {
+    int orall = pat[0];
+    if (JPT == 2) orall |= pat[1];
+    if (JPT == 4) orall = or3(or3(pat[0], pat[1], pat[2]), pat[3], 0);
+    if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
+      // rare path: the reference's own rounded comparisons for every output still running
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
-        if (livemask[m] && have_prev && ratio_gt(ysum[m], wsum[m], xprev) && ratio_le(ysum[m], wsum[m], x)) {
-          livemask[m] = 0;  // spike lies in (previous input, x]: freeze the sums
+        const bool fire = (livemask[m] != 0) & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
+        if (fire) {
+          livemask[m] = 0;  // spike lies in (previous input, x]: keep the sums aside ...
           wfin[m] = wsum[m];
           yfin[m] = ysum[m];
+          // ... and park the running ones where the pattern can never show again: with wsum = +inf
+          // both a and d stay -inf, which reads as "not armed" at every later step
+          wsum[m] = CUDART_INF_F;
         }
       }
     }
@@ -114,7 +133,6 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       ysum[m] = fmaf(x, wv[m], ysum[m]);
     }
     xprev = x;
-    have_prev = true;
   };
 
   int k = 0;
@@ -155,7 +173,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     float ws = wfin[m], ys = yfin[m];
     if (livemask[m]) {
       ws = wsum[m]; ys = ysum[m];
-      fired = have_prev && ratio_gt(ys, ws, xprev);
+      fired = ratio_gt(ys, ws, xprev);
     }
     float yv = g.maxv, iv = 0.f;
     if (fired) {
