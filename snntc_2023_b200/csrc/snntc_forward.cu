@@ -190,22 +190,44 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
 }
 
 // ------------------------------------------------------------------------------------------- gather
+// Where element i = lane + 32*n of a conv row sits in the receptive field, kept incrementally so that
+// the per-element work has no integer division (the lane -> (kh, kw, c) map is the same for every row).
+struct TapCursor {
+  int kh, kw, c;
+  __device__ __forceinline__ void init(const Geometry& g, int lane) {
+    const int tap = lane / g.C;
+    c = lane - tap * g.C;
+    kh = tap / g.Kw;
+    kw = tap - kh * g.Kw;
+  }
+  __device__ __forceinline__ void advance32(const Geometry& g) {
+    c += 32;
+    while (c >= g.C) {
+      c -= g.C;
+      if (++kw == g.Kw) { kw = 0; ++kh; }
+    }
+  }
+};
+
 // Loads one row, drops inputs above MAX-0.1, writes packed keys to dst[0..n) in index order and
 // (if hist != nullptr) counts the four 8-bit digits of every kept key. Returns n. One warp.
+// `start` is the cursor of element `lane` (conv only).
 __device__ __forceinline__ int gather_row(const Geometry& g, const float* __restrict__ x, int r, int lane,
-                                          u64* __restrict__ dst, unsigned* __restrict__ hist) {
+                                          u64* __restrict__ dst, unsigned* __restrict__ hist, const TapCursor& start) {
   const int I = g.I;
   const float maxcomp = g.maxv - 0.1f;
   int n = 0;
-  int b = 0, h0 = 0, w0 = 0;
+  int h0 = 0, w0 = 0;
   const float* xr = x + (size_t)r * I;
+  TapCursor cur = start;
   if (g.is_conv) {
     const int nw = r % g.Nw;
     const int t = r / g.Nw;
     const int nh = t % g.Nh;
-    b = t / g.Nh;
+    const int b = t / g.Nh;
     h0 = nh * g.Sh - g.pad_top;
     w0 = nw * g.Sw - g.pad_left;
+    xr = x + (size_t)b * g.H * g.W * g.C;
   }
   for (int i0 = 0; i0 < I; i0 += 32) {
     const int i = i0 + lane;
@@ -214,12 +236,11 @@ __device__ __forceinline__ int gather_row(const Geometry& g, const float* __rest
       if (!g.is_conv) {
         v = __ldg(xr + i);
       } else {
-        const int tap = i / g.C, c = i - tap * g.C;
-        const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
-        const int h = h0 + kh, ww = w0 + kw;
-        if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v = __ldg(x + (((size_t)b * g.H + h) * g.W + ww) * g.C + c);
+        const int h = h0 + cur.kh, ww = w0 + cur.kw;
+        if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v = __ldg(xr + ((size_t)h * g.W + ww) * g.C + cur.c);
       }
     }
+    if (g.is_conv) cur.advance32(g);
     const bool keep = (i < I) && !(v > maxcomp);
     const unsigned mask = __ballot_sync(0xffffffffu, keep);
     if (keep) {
@@ -335,10 +356,12 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
   u64* a = reinterpret_cast<u64*>(mine);
   u64* b = a + I;
   unsigned* hist = reinterpret_cast<unsigned*>(b + I);
+  TapCursor start = {0, 0, 0};
+  if (g.is_conv) start.init(g, lane);
   for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
     for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
     __syncwarp();
-    const int n = gather_row(g, x, r, lane, a, hist);
+    const int n = gather_row(g, x, r, lane, a, hist, start);
     __syncwarp();
     const u64* res;
     if (n <= 32) { sort_small(a, b, n, lane); res = b; }
@@ -364,7 +387,9 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* _
   const int tid = threadIdx.x;
   for (int r = blockIdx.x; r < g.R; r += gridDim.x) {
     if (tid < 32) {
-      const int n = gather_row(g, x, r, tid, keys, nullptr);
+      TapCursor start = {0, 0, 0};
+      if (g.is_conv) start.init(g, tid);
+      const int n = gather_row(g, x, r, tid, keys, nullptr, start);
       if (tid == 0) s_n = n;
     }
     __syncthreads();
