@@ -145,6 +145,8 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *   snntc_launch_count            kernels launched by this library since it was loaded
  *   snntc_profile_backward_parts  bit 0: run the dX kernel, bit 1: run the dW kernels (default 3);
  *                                 lets a profiler time the two halves of a backward call apart
+ *   snntc_profile_forward_parts   bit 0: run the sort kernel, bit 1: run the walk kernel (default 3); with 1 the
+ *                                 outputs are not written -- for timing the sort alone
  *   snntc_set_overlap             1 (default): independent kernels of one call (sort of the next block of
  *                                 rows / walk of the current one; dX / dW) are forked onto one library-owned
  *                                 auxiliary stream per device and joined back with events, the caller still
@@ -155,6 +157,7 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  */
 SNNTC_API unsigned long long snntc_launch_count(void);
 SNNTC_API void snntc_profile_backward_parts(int mask);
+SNNTC_API void snntc_profile_forward_parts(int mask);
 SNNTC_API void snntc_set_overlap(int on);
 SNNTC_API int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream);
 

@@ -26,6 +26,7 @@ SYMBOLS = {
     "snntc_cv_backward": (_INT, [_F] * 8 + [_INT] * 10 + [_F, _SZ, _F]),
     "snntc_launch_count": (ctypes.c_ulonglong, []),
     "snntc_profile_backward_parts": (None, [_INT]),
+    "snntc_profile_forward_parts": (None, [_INT]),
     "snntc_set_overlap": (None, [_INT]),
     "snntc_fp32_probe": (_INT, [_F, _INT, _INT, ctypes.POINTER(ctypes.c_double), _F]),
     "snntc_minpool_forward": (_INT, [_F, _F, _F] + [_INT] * 12 + [ctypes.c_float, _F]),

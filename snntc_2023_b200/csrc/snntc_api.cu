@@ -13,6 +13,7 @@
 namespace snntc {
 static std::atomic<unsigned long long> g_launches{0};
 static std::atomic<int> g_backward_parts{3};
+static std::atomic<int> g_forward_parts{3};
 static std::atomic<int> g_overlap{1};
 static std::mutex g_aux_mutex;
 static AuxStream g_aux[64];
@@ -36,6 +37,7 @@ AuxStream* aux_stream() {
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
 int backward_parts() { return g_backward_parts.load(std::memory_order_relaxed); }
+int forward_parts() { return g_forward_parts.load(std::memory_order_relaxed); }
 }  // namespace snntc
 
 namespace {
@@ -176,6 +178,8 @@ const char* snntc_version(void) { return "snntc_b200 0.1 sm_100a"; }
 unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std::memory_order_relaxed); }
 
 void snntc_set_overlap(int on) { snntc::g_overlap.store(on ? 1 : 0, std::memory_order_relaxed); }
+
+void snntc_profile_forward_parts(int mask) { snntc::g_forward_parts.store(mask & 3, std::memory_order_relaxed); }
 
 void snntc_profile_backward_parts(int mask) { snntc::g_backward_parts.store(mask & 3, std::memory_order_relaxed); }
 

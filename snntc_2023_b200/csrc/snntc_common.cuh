@@ -29,6 +29,8 @@ struct LaunchInfo {
 void count_launch(int n = 1);
 // profiling aid: bit 0 = run the dX kernel, bit 1 = run the dW kernels (default 3)
 int backward_parts();
+// profiling aid: bit 0 = run the sort kernel, bit 1 = run the walk kernel (default 3)
+int forward_parts();
 
 // One auxiliary stream and a few events per device, created on first use and kept for the life of the
 // process. Kernels of one call that do not depend on each other (the sort of the next block of rows

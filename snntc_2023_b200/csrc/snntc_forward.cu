@@ -460,7 +460,9 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   int* nvalid_g = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + keys_bytes(g));
   const int istride = key_stride(g);
 
+  const int fparts = forward_parts();
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
+    if (!(fparts & 2)) return OK;
     if (g.J <= 32) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     if (g.J <= 64) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
@@ -500,7 +502,7 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
 
   // The sort is bound by shared-memory latency and integer work, the walk by FP32 issue and L1: run
   // block c+1's sort beside block c's walk. Sorts go to the auxiliary stream, walks stay on the caller's.
-  AuxStream* aux = g.R >= 8 * li.num_sms ? aux_stream() : nullptr;
+  AuxStream* aux = (g.R >= 8 * li.num_sms && fparts == 3) ? aux_stream() : nullptr;
   const int nblocks = aux ? 4 : 1;
   if (!aux) {
     int rc = sort(s, 0, g.R);
