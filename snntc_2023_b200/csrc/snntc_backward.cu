@@ -219,6 +219,160 @@ snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------- dX, wide tile
+// Same computation as snn_dx_kernel for J % 4 == 0, with a 128-point x 64-channel CTA tile and 8x4
+// outputs per thread: 32 independent compare/FMA pairs per output column instead of 16, which is what
+// hides the compare -> predicated-FMA latency at two CTAs per SM. Shared-memory tiles are stored
+// transposed ([j][point], [j][channel]) so that a thread reads its 8 points / 4 channels with 16-byte loads.
+constexpr int kWideP = 128;
+constexpr int kYStride = kWideP + 4;
+constexpr int kWStride = kTile + 4;
+
+__global__ void __launch_bounds__(kBwdThreads)
+snn_dx_wide_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
+                   const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
+  __shared__ __align__(16) float Ys[2][kJT * kYStride];
+  __shared__ __align__(16) float Us[2][kJT * kYStride];
+  __shared__ __align__(16) float Ws[2][kJT * kWStride];
+  __shared__ int s_pb[kWideP], s_ph[kWideP], s_pw[kWideP];
+
+  const int J = g.J;
+  const int CH = g.is_conv ? g.C : g.I;
+  const int P = g.is_conv ? g.B * g.H * g.W : g.R;
+  const int taps = g.is_conv ? g.Kh * g.Kw : 1;
+  const int njt = (J + kJT - 1) / kJT;
+  const int ntiles = taps * njt;
+  const float* __restrict__ yv = out;
+
+  const int tid = threadIdx.x;
+  const int tp = tid >> 4, tc = tid & 15;
+  const int p0 = blockIdx.x * kWideP, c0 = blockIdx.y * kTile;
+
+  if (tid < kWideP) {
+    const int p = p0 + tid;
+    int pb = -1, ph = 0, pw = 0;
+    if (p < P) {
+      if (!g.is_conv) {
+        pb = p;
+      } else {
+        const int ww = p % g.W;
+        const int t = p / g.W;
+        pb = t / g.H;
+        ph = t % g.H + g.pad_top;
+        pw = ww + g.pad_left;
+      }
+    }
+    s_pb[tid] = pb; s_ph[tid] = ph; s_pw[tid] = pw;
+  }
+
+  float xr[8][4], acc[8][4];
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int p = p0 + 8 * tp + a, c = c0 + 4 * tc + b;
+      xr[a][b] = (p < P && c < CH) ? __ldg(x + (size_t)p * CH + c) : CUDART_INF_F;
+      acc[a][b] = 0.f;
+    }
+  __syncthreads();
+
+  // loaders: y/u -> rows (tid >> 2) and (tid >> 2) + 64, columns 4*(tid & 3); w -> channel row (tid >> 2)
+  const int ld_jj = (tid & 3) * 4, ld_row = tid >> 2;
+  float4 py[2], pu[2], pwv;
+
+  auto out_row = [&](int row, int kh, int kw) -> int {
+    int orow = s_pb[row];
+    if (g.is_conv && orow >= 0) {
+      const int hh = s_ph[row] - kh, wq = s_pw[row] - kw;
+      int nh = hh, nw = wq;
+      bool ok = hh >= 0 && wq >= 0;
+      if (g.Sh != 1 || g.Sw != 1) {
+        nh = hh / g.Sh; nw = wq / g.Sw;
+        ok = ok && nh * g.Sh == hh && nw * g.Sw == wq;
+      }
+      ok = ok && nh < g.Nh && nw < g.Nw;
+      orow = ok ? (orow * g.Nh + nh) * g.Nw + nw : -1;
+    }
+    return orow;
+  };
+  auto fetch = [&](int t) {
+    const int tap = t / njt;
+    const int j = (t - tap * njt) * kJT + ld_jj;
+    int kh = 0, kw = 0;
+    if (g.is_conv) { kh = tap / g.Kw; kw = tap - kh * g.Kw; }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int orow = out_row(ld_row + 64 * q, kh, kw);
+      py[q] = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      pu[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (orow >= 0 && j < J) {
+        const size_t o = (size_t)orow * J + j;
+        py[q] = __ldg(reinterpret_cast<const float4*>(yv + o));
+        pu[q] = __ldg(reinterpret_cast<const float4*>(uv + o));
+      }
+    }
+    pwv = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int c = c0 + ld_row;
+    if (c < CH && j < J) pwv = __ldg(reinterpret_cast<const float4*>(w + ((size_t)tap * CH + c) * J + j));
+  };
+  auto park = [&](int buf) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int row = ld_row + 64 * q;
+      Ys[buf][(ld_jj + 0) * kYStride + row] = py[q].x; Us[buf][(ld_jj + 0) * kYStride + row] = pu[q].x;
+      Ys[buf][(ld_jj + 1) * kYStride + row] = py[q].y; Us[buf][(ld_jj + 1) * kYStride + row] = pu[q].y;
+      Ys[buf][(ld_jj + 2) * kYStride + row] = py[q].z; Us[buf][(ld_jj + 2) * kYStride + row] = pu[q].z;
+      Ys[buf][(ld_jj + 3) * kYStride + row] = py[q].w; Us[buf][(ld_jj + 3) * kYStride + row] = pu[q].w;
+    }
+    Ws[buf][(ld_jj + 0) * kWStride + ld_row] = pwv.x;
+    Ws[buf][(ld_jj + 1) * kWStride + ld_row] = pwv.y;
+    Ws[buf][(ld_jj + 2) * kWStride + ld_row] = pwv.z;
+    Ws[buf][(ld_jj + 3) * kWStride + ld_row] = pwv.w;
+  };
+
+  fetch(0);
+  park(0);
+  __syncthreads();
+
+  for (int t = 0; t < ntiles; ++t) {
+    const int buf = t & 1;
+    if (t + 1 < ntiles) fetch(t + 1);
+
+#pragma unroll
+    for (int jj = 0; jj < kJT; ++jj) {
+      const float4 ya = *reinterpret_cast<const float4*>(&Ys[buf][jj * kYStride + 8 * tp]);
+      const float4 yb = *reinterpret_cast<const float4*>(&Ys[buf][jj * kYStride + 8 * tp + 4]);
+      const float4 ua = *reinterpret_cast<const float4*>(&Us[buf][jj * kYStride + 8 * tp]);
+      const float4 ub = *reinterpret_cast<const float4*>(&Us[buf][jj * kYStride + 8 * tp + 4]);
+      const float4 w4 = *reinterpret_cast<const float4*>(&Ws[buf][jj * kWStride + 4 * tc]);
+      const float y8[8] = {ya.x, ya.y, ya.z, ya.w, yb.x, yb.y, yb.z, yb.w};
+      const float u8[8] = {ua.x, ua.y, ua.z, ua.w, ub.x, ub.y, ub.z, ub.w};
+      const float wv[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+      for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) masked_fma(acc[a][b], xr[a][b], y8[a], u8[a], wv[b]);
+    }
+
+    if (t + 1 < ntiles) park(buf ^ 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int a = 0; a < 8; ++a) {
+    const int p = p0 + 8 * tp + a, c = c0 + 4 * tc;
+    if (p < P) {
+      if (c + 3 < CH && (CH & 3) == 0) {
+        *reinterpret_cast<float4*>(dx + (size_t)p * CH + c) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+      } else {
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          if (c + b < CH) dx[(size_t)p * CH + c + b] = acc[a][b];
+      }
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------- dW
 // Output tile 128 (fan-in rows i, bias row included) x 64 (outputs j), 8x4 per thread; blockIdx.z
 // selects a slice of the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane
@@ -449,8 +603,14 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    if (vec) snn_dx_kernel<true><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
-    else snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    if (vec && P >= 64 * kWideP) {
+      dim3 gridw((unsigned)((P + kWideP - 1) / kWideP), (CH + kTile - 1) / kTile);
+      snn_dx_wide_kernel<<<gridw, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    } else if (vec) {
+      snn_dx_kernel<true><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    } else {
+      snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    }
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
     if (aux && cudaEventRecord(aux->join[0], aux->stream) != cudaSuccess) return E_CUDA;
