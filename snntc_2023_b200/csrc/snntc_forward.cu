@@ -229,31 +229,42 @@ __device__ __forceinline__ int gather_row(const Geometry& g, const float* __rest
     w0 = nw * g.Sw - g.pad_left;
     xr = x + (size_t)b * g.H * g.W * g.C;
   }
-  for (int i0 = 0; i0 < I; i0 += 32) {
-    const int i = i0 + lane;
-    float v = g.maxv;
-    if (i < I) {
-      if (!g.is_conv) {
-        v = __ldg(xr + i);
-      } else {
-        const int h = h0 + cur.kh, ww = w0 + cur.kw;
-        if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v = __ldg(xr + ((size_t)h * g.W + ww) * g.C + cur.c);
+  // four loads in flight per lane before anything depends on them: the loop is otherwise one global
+  // load latency per 32 elements
+  constexpr int kBatch = 4;
+  for (int i0 = 0; i0 < I; i0 += 32 * kBatch) {
+    float v[kBatch];
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      const int i = i0 + 32 * q + lane;
+      v[q] = g.maxv;
+      if (i < I) {
+        if (!g.is_conv) {
+          v[q] = __ldg(xr + i);
+        } else {
+          const int h = h0 + cur.kh, ww = w0 + cur.kw;
+          if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v[q] = __ldg(xr + ((size_t)h * g.W + ww) * g.C + cur.c);
+        }
       }
+      if (g.is_conv) cur.advance32(g);
     }
-    if (g.is_conv) cur.advance32(g);
-    const bool keep = (i < I) && !(v > maxcomp);
-    const unsigned mask = __ballot_sync(0xffffffffu, keep);
-    if (keep) {
-      const uint32_t key = float_to_sortable(v);
-      dst[n + __popc(mask & ((1u << lane) - 1u))] = ((u64)key << 32) | (uint32_t)i;
-      if (hist) {
-        atomicAdd(&hist[key & 255u], 1u);
-        atomicAdd(&hist[256 + ((key >> 8) & 255u)], 1u);
-        atomicAdd(&hist[512 + ((key >> 16) & 255u)], 1u);
-        atomicAdd(&hist[768 + (key >> 24)], 1u);
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      const int i = i0 + 32 * q + lane;
+      const bool keep = (i < I) && !(v[q] > maxcomp);
+      const unsigned mask = __ballot_sync(0xffffffffu, keep);
+      if (keep) {
+        const uint32_t key = float_to_sortable(v[q]);
+        dst[n + __popc(mask & ((1u << lane) - 1u))] = ((u64)key << 32) | (uint32_t)i;
+        if (hist) {
+          atomicAdd(&hist[key & 255u], 1u);
+          atomicAdd(&hist[256 + ((key >> 8) & 255u)], 1u);
+          atomicAdd(&hist[512 + ((key >> 16) & 255u)], 1u);
+          atomicAdd(&hist[768 + (key >> 24)], 1u);
+        }
       }
+      n += __popc(mask);
     }
-    n += __popc(mask);
   }
   return n;
 }
@@ -296,19 +307,34 @@ __device__ __forceinline__ u64* radix_sort_row(u64* a, u64* b, int n, unsigned* 
     for (int q = 0; q < 8; ++q) { h[lane * 8 + q] = run; run += c[q]; }
     __syncwarp();
     const int shift = 32 + 8 * p;
-    for (int i0 = 0; i0 < n; i0 += 32) {
-      const int i = i0 + lane;
-      const bool act = i < n;
-      const u64 e = act ? src[i] : 0ull;
-      const unsigned d = act ? (unsigned)(e >> shift) & 255u : 256u + (unsigned)lane;
-      const unsigned peers = __match_any_sync(0xffffffffu, d);
-      const unsigned before = peers & lt;
-      unsigned off = 0;
-      if (act) off = h[d];
-      __syncwarp();
-      if (act && before == 0) h[d] = off + __popc(peers);
-      __syncwarp();
-      if (act) dst[off + __popc(before)] = e;
+    // four batches of 32 keys at a time: their loads and digit matches do not depend on the running bin
+    // offsets, only the short read-offset / bump-bin sequence per batch is serial
+    constexpr int kSB = 4;
+    for (int i0 = 0; i0 < n; i0 += 32 * kSB) {
+      u64 e[kSB];
+      unsigned d[kSB], peers[kSB];
+      bool act[kSB];
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) {
+        const int i = i0 + 32 * q + lane;
+        act[q] = i < n;
+        e[q] = act[q] ? src[i] : 0ull;
+        d[q] = act[q] ? (unsigned)(e[q] >> shift) & 255u : 256u + (unsigned)lane;
+      }
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) peers[q] = __match_any_sync(0xffffffffu, d[q]);
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) {
+        if (i0 + 32 * q < n) {   // warp-uniform
+          const unsigned before = peers[q] & lt;
+          unsigned off = 0;
+          if (act[q]) off = h[d[q]];
+          __syncwarp();
+          if (act[q] && before == 0) h[d[q]] = off + __popc(peers[q]);
+          __syncwarp();
+          if (act[q]) dst[off + __popc(before)] = e[q];
+        }
+      }
     }
     __syncwarp();
     u64* t = src; src = dst; dst = t;
