@@ -11,9 +11,9 @@
 //   3. walk (walk kernel): every warp takes (row, block of 32*JPT outputs) items; lanes span
 //      consecutive output columns so each weight-row read is one coalesced 128-byte line. The running
 //      sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the arithmetic
-//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is a sign
-//      pattern of ysum - x*wsum per step, backed by the reference's exact division-free comparisons
-//      whenever the pattern shows up in any lane (see walk_row).
+//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is the sign of
+//      ysum - x*wsum per step, backed by the reference's exact division-free comparisons whenever it
+//      turns non-positive in any lane (see walk_row).
 #include "snntc_common.cuh"
 
 #include <math_constants.h>
@@ -49,26 +49,23 @@ __device__ __forceinline__ bool ratio_le(float ysum, float wsum, float c) {
   return ya <= c * wa;
 }
 
-// sign bit set iff a has the sign of wsum and d has not: ~(a ^ wsum) & (d ^ wsum), as one LOP3
-__device__ __forceinline__ int fire_pattern(float a, float wsum, float d) {
-  int r;
-  asm("lop3.b32 %0, %1, %2, %3, 0x42;" : "=r"(r) : "r"(__float_as_int(a)), "r"(__float_as_int(wsum)), "r"(__float_as_int(d)));
-  return r;
-}
 __device__ __forceinline__ int or3(int a, int b, int c) {
   int r;
   asm("lop3.b32 %0, %1, %2, %3, 0xFE;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
   return r;
 }
 
-// One warp walks one row for 32*JPT outputs (lane + 32*m). Per step and output the loop itself only
-// does the two running sums plus a = ysum - xprev*wsum, d = ysum - x*wsum and a sign test: a fire
-// before consuming x means "ysum/wsum > previous input" and "ysum/wsum <= x", i.e. sign(wsum)*a > 0 >=
-// sign(wsum)*d. When any lane sees that pattern, the warp evaluates the reference's own rounded,
-// division-free tests for every output still running at this step, so the decision is the
-// reference's; the cheap pattern (exact signs from two FMAs) and the reference's test (rounded
-// products) can disagree only when a or d is within an ulp of zero, i.e. when the spike time is tied
-// with an input to the last bit.
+// One warp walks one row for 32*JPT outputs (lane + 32*m). Let q_k = ysum - x_k*wsum be taken just
+// before input k is consumed. The reference fires at step k when "ysum/wsum > previous input" and
+// "ysum/wsum <= x_k", i.e. sign(wsum)*q_{k-1} > 0 >= sign(wsum)*q_k (q_{k-1} re-evaluated with the sums
+// of step k, which leaves its value unchanged). q starts positive (theta*x_0, or theta*biasvolt with
+// bias) and moves by -(x_k - x_{k-1})*wsum per step, so a change of sign can only happen in the
+// direction that sign(wsum) allows: the FIRST fire is simply the first k with q_k <= 0. The loop
+// therefore computes one extra FMA per output and step (q, with its exact sign), ORs the sign bits and
+// takes one warp vote; only when some lane sees q <= 0 does the warp evaluate the reference's own
+// rounded, division-free tests for the outputs concerned, so the decision is the reference's. An output
+// whose q is non-positive but which the reference test did not fire (possible only when q is within an
+// ulp of zero) keeps being tested exactly at every following step.
 template <int JPT, int CH, bool FULL>
 __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
@@ -100,30 +97,26 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
 
   const float* wl = w + (FULL ? jbase + lane : 0);
 
-  // one step for all JPT outputs of this lane: pattern test, (rarely) exact test, then consume
+  // one step for all JPT outputs of this lane: sign test, (rarely) exact test, then consume
   auto step = [&](const float x, const float (&wv)[JPT]) {
-    int pat[JPT];
+    int q[JPT];
 #pragma unroll
-    for (int m = 0; m < JPT; ++m) {
-      const float a = fmaf(-xprev, wsum[m], ysum[m]);
-      const float d = fmaf(-x, wsum[m], ysum[m]);
-      pat[m] = fire_pattern(a, wsum[m], d);
-    }
-    int orall = pat[0];
-    if (JPT == 2) orall |= pat[1];
-    if (JPT == 4) orall = or3(or3(pat[0], pat[1], pat[2]), pat[3], 0);
+    for (int m = 0; m < JPT; ++m) q[m] = __float_as_int(fmaf(-x, wsum[m], ysum[m]));
+    int orall = q[0];
+    if (JPT == 2) orall |= q[1];
+    if (JPT == 4) orall = or3(or3(q[0], q[1], q[2]), q[3], 0);
     if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
-      // rare path: the reference's own rounded comparisons for every output still running
+      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
-        const bool fire = (livemask[m] != 0) & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
+        const bool fire = (q[m] < 0) & (livemask[m] != 0) & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
         if (fire) {
           livemask[m] = 0;  // spike lies in (previous input, x]: keep the sums aside ...
           wfin[m] = wsum[m];
           yfin[m] = ysum[m];
-          // ... and park the running ones where the pattern can never show again: with wsum = +inf
-          // both a and d stay -inf, which reads as "not armed" at every later step
-          wsum[m] = CUDART_INF_F;
+          // ... and park the running ones where q can never be negative again: with wsum = -inf,
+          // q = ysum + x*inf = +inf at every later step
+          wsum[m] = -CUDART_INF_F;
         }
       }
     }
