@@ -510,7 +510,7 @@ def run_gpu_arm(args):
         wl.step(resident[i % nb])
     torch.cuda.synchronize()
     graph_note = None
-    if kind == "net" and not args.no_graph:
+    if kind == "net" and not args.no_graph and world == 1:   # multi-GPU steps keep eager launches (collective inside)
         try:
             wl.enable_graph(resident[0])
             for i in range(3):
