@@ -147,10 +147,10 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *                                 lets a profiler time the two halves of a backward call apart
  *   snntc_profile_forward_parts   bit 0: run the sort kernel, bit 1: run the walk kernel (default 3); with 1 the
  *                                 outputs are not written -- for timing the sort alone
- *   snntc_set_overlap             1 (default): independent kernels of one call (sort of the next block of
- *                                 rows / walk of the current one; dX / dW) are forked onto one library-owned
- *                                 auxiliary stream per device and joined back with events, the caller still
- *                                 sees plain stream order; 0: everything runs on the caller's stream
+ *   snntc_set_overlap             1 (default): the two independent kernels of a backward call (dX, dW) run side
+ *                                 by side, dX on one library-owned auxiliary stream per device that is joined
+ *                                 back with events, so the caller still sees plain stream order; 0: everything
+ *                                 runs on the caller's stream
  *   snntc_fp32_probe              queues `ctas` CTAs of 256 threads running `iters` rounds of 8
  *                                 independent FMAs each and reports the flop count: timed by the
  *                                 caller, it gives the FP32 issue ceiling the kernels are judged against

@@ -33,9 +33,8 @@ int backward_parts();
 int forward_parts();
 
 // One auxiliary stream and a few events per device, created on first use and kept for the life of the
-// process. Kernels of one call that do not depend on each other (the sort of the next block of rows
-// and the walk of the current one; dX and dW) are forked onto it and joined back into the caller's
-// stream with events, so the caller still sees ordinary stream order. Returns nullptr when the
+// process. Kernels of one call that do not depend on each other (dX and dW) are forked onto it and
+// joined back into the caller's stream with events, so the caller still sees ordinary stream order. Returns nullptr when the
 // resources cannot be created or overlap is switched off (snntc_set_overlap(0)): callers then run
 // everything on the one stream.
 struct AuxStream {

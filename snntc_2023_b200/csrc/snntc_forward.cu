@@ -135,7 +135,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     float wv[CH][JPT];
 #pragma unroll
     for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = ents[k + u];
+      const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
       xs[u] = __uint_as_float(e.x);
       const float* wrow = wl + e.y;
 #pragma unroll
@@ -150,7 +150,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   }
   if (!all_done) {
     for (; k < nvalid; ++k) {
-      const WalkEntry e = ents[k];
+      const WalkEntry e = __ldcg(ents + k);
       const float* wrow = wl + e.y;
       float wv[JPT];
 #pragma unroll
@@ -378,9 +378,12 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
   TapCursor start = {0, 0, 0};
   if (g.is_conv) start.init(g, lane);
   for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
-    for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
-    __syncwarp();
-    const int n = gather_row(g, x, r, lane, a, hist, start);
+    const bool tiny = I <= 32;   // ranked with shuffles: no digit histograms needed
+    if (!tiny) {
+      for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
+      __syncwarp();
+    }
+    const int n = gather_row(g, x, r, lane, a, tiny ? nullptr : hist, start);
     __syncwarp();
     const u64* res;
     if (n <= 32) { sort_small(a, b, n, lane); res = b; }
@@ -480,10 +483,32 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   const int istride = key_stride(g);
 
   const int fparts = forward_parts();
+  // Outputs per lane (JPT): more of them amortise the per-step cost (list entry, address, vote) over more
+  // outputs, fewer give more (row, output block) items to spread over the SMs. Measured instructions per
+  // warp-step are about 19 / 24 / 39 for JPT 1 / 2 / 4 and 6 / 4 / 3 CTAs fit per SM; pick the smallest
+  // estimate of (waves of items) x (cost of a step).
+  int jpt = g.J <= 32 ? 1 : (g.J <= 64 ? 2 : 4);   // many items: most outputs per lane the row can fill
+  {
+    const double cost[3] = {19.0, 24.0, 39.0};
+    const int ctas[3] = {6, 4, 3};
+    const int top = jpt == 1 ? 0 : (jpt == 2 ? 1 : 2);
+    const double items_top = (double)g.R * ((g.J + 32 * jpt - 1) / (32 * jpt));
+    if (items_top < 4.0 * li.num_sms * ctas[top] * kFwdWarps) {
+      // few items: whole waves of items matter, pick the smallest (waves) x (cost of a step)
+      double best = 0;
+      for (int c = 0; c <= top; ++c) {
+        const int cand = 1 << c;
+        const double items = (double)g.R * ((g.J + 32 * cand - 1) / (32 * cand));
+        const double slots = (double)li.num_sms * ctas[c] * kFwdWarps;
+        const double est = (double)(long)(items / slots + 0.999) * cost[c];
+        if (c == 0 || est < best) { best = est; jpt = cand; }
+      }
+    }
+  }
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (g.J <= 32) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    if (g.J <= 64) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (jpt == 1) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (jpt == 2) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
   };
 
@@ -502,11 +527,18 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     return walk(s, 0, g.R);
   }
 
-  int wpc = (int)(budget / per_warp);
-  if (wpc > kFwdWarps) wpc = kFwdWarps;
-  int ctas_per_sm = (int)(budget / (per_warp * wpc));   // short rows: several CTAs per SM instead of one fat CTA
-  if (ctas_per_sm > 4) ctas_per_sm = 4;
-  if (ctas_per_sm < 1) ctas_per_sm = 1;
+  // warps per CTA and CTAs per SM: the combination that keeps the most rows (warps) resident per SM
+  int wpc = 1, ctas_per_sm = 1;
+  {
+    int best = 0;
+    for (int cand = kFwdWarps; cand >= 1; --cand) {
+      if (per_warp * cand > budget) continue;
+      int c = (int)(((size_t)li.max_smem_optin) / (per_warp * cand + 1024));
+      if (c > 4) c = 4;
+      if (c < 1) c = 1;
+      if (cand * c > best) { best = cand * c; wpc = cand; ctas_per_sm = c; }
+    }
+  }
   const size_t smem = per_warp * wpc;
   if (cudaFuncSetAttribute(snn_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
     return E_CUDA;
@@ -519,29 +551,11 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
   };
 
-  // The sort is bound by shared-memory latency and integer work, the walk by FP32 issue and L1: run
-  // block c+1's sort beside block c's walk. Sorts go to the auxiliary stream, walks stay on the caller's.
-  AuxStream* aux = (g.R >= 8 * li.num_sms && fparts == 3) ? aux_stream() : nullptr;
-  const int nblocks = aux ? 4 : 1;
-  if (!aux) {
-    int rc = sort(s, 0, g.R);
-    if (rc != OK) return rc;
-    return walk(s, 0, g.R);
-  }
-  if (cudaEventRecord(aux->fork, s) != cudaSuccess || cudaStreamWaitEvent(aux->stream, aux->fork, 0) != cudaSuccess)
-    return E_CUDA;
-  const int per = (g.R + nblocks - 1) / nblocks;
-  for (int c = 0; c < nblocks; ++c) {
-    const int r0 = c * per, r1 = r0 + per < g.R ? r0 + per : g.R;
-    if (r0 >= r1) break;
-    int rc = sort(aux->stream, r0, r1);
-    if (rc != OK) return rc;
-    if (cudaEventRecord(aux->join[c], aux->stream) != cudaSuccess || cudaStreamWaitEvent(s, aux->join[c], 0) != cudaSuccess)
-      return E_CUDA;
-    rc = walk(s, r0, r1);
-    if (rc != OK) return rc;
-  }
-  return OK;
+  // Sort, then walk, on the caller's stream. (Running the next block's sort beside the current block's walk
+  // on a second stream was measured and gains nothing: both kernels fill the SMs on their own.)
+  int rc = (fparts & 1) ? sort(s, 0, g.R) : OK;
+  if (rc != OK) return rc;
+  return walk(s, 0, g.R);
 }
 
 }  // namespace snntc
