@@ -2,9 +2,9 @@
 //
 // Rows are dense samples or conv receptive fields (gathered straight from the NHWC image with MAX
 // outside it). Two kernels, joined by a scratch buffer of sorted keys in global memory:
-//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest are packed as
-//      (sortable value bits << 32 | source index) in shared memory while four 8-bit digit histograms
-//      of the value bits are built;
+//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest are kept as
+//      32-bit sortable value bits plus a 16-bit source index in shared memory while four 8-bit digit
+//      histograms of the value bits are built;
 //   2. sort: a stable least-significant-digit radix sort by the warp (digit passes in which every key
 //      falls in one bin are skipped), O(n) per row; rows of <= 32 inputs are ranked with shuffles,
 //      rows too long for two shared-memory buffers fall back to an in-place bitonic network;
@@ -24,7 +24,6 @@ namespace {
 
 constexpr int kFwdThreads = 256;
 constexpr int kFwdWarps = kFwdThreads / 32;
-constexpr int kHistWords = 4 * 256;  // per warp
 
 typedef unsigned long long u64;
 
@@ -263,78 +262,6 @@ __device__ __forceinline__ int gather_row(const Geometry& g, const float* __rest
 }
 
 // ------------------------------------------------------------------------------------------- sorts
-// n <= 32: rank every key against the others with shuffles. src -> dst, one warp.
-__device__ __forceinline__ void sort_small(const u64* __restrict__ src, u64* __restrict__ dst, int n, int lane) {
-  const u64 e = lane < n ? src[lane] : ~0ull;
-  int rank = 0;
-  for (int j = 0; j < n; ++j) {
-    const u64 o = __shfl_sync(0xffffffffu, e, j);
-    rank += o < e;  // keys are unique (the index is part of them)
-  }
-  if (lane < n) dst[rank] = e;
-}
-
-// Stable LSD radix sort of n keys by their upper 32 bits, 8 bits per pass, one warp. hist holds the
-// four digit histograms on entry. Returns the buffer that holds the sorted keys.
-__device__ __forceinline__ u64* radix_sort_row(u64* a, u64* b, int n, unsigned* hist, int lane) {
-  u64* src = a;
-  u64* dst = b;
-  const unsigned lt = (1u << lane) - 1u;
-#pragma unroll 1
-  for (int p = 0; p < 4; ++p) {
-    unsigned* h = hist + 256 * p;
-    // exclusive scan of the 256 bins (8 per lane); a pass whose keys all share one digit is skipped
-    unsigned c[8], s = 0;
-    bool single = false;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) { c[q] = h[lane * 8 + q]; single |= (c[q] == (unsigned)n); s += c[q]; }
-    if (__any_sync(0xffffffffu, single)) continue;
-    unsigned incl = s;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += o;
-    }
-    unsigned run = incl - s;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) { h[lane * 8 + q] = run; run += c[q]; }
-    __syncwarp();
-    const int shift = 32 + 8 * p;
-    // four batches of 32 keys at a time: their loads and digit matches do not depend on the running bin
-    // offsets, only the short read-offset / bump-bin sequence per batch is serial
-    constexpr int kSB = 4;
-    for (int i0 = 0; i0 < n; i0 += 32 * kSB) {
-      u64 e[kSB];
-      unsigned d[kSB], peers[kSB];
-      bool act[kSB];
-#pragma unroll
-      for (int q = 0; q < kSB; ++q) {
-        const int i = i0 + 32 * q + lane;
-        act[q] = i < n;
-        e[q] = act[q] ? src[i] : 0ull;
-        d[q] = act[q] ? (unsigned)(e[q] >> shift) & 255u : 256u + (unsigned)lane;
-      }
-#pragma unroll
-      for (int q = 0; q < kSB; ++q) peers[q] = __match_any_sync(0xffffffffu, d[q]);
-#pragma unroll
-      for (int q = 0; q < kSB; ++q) {
-        if (i0 + 32 * q < n) {   // warp-uniform
-          const unsigned before = peers[q] & lt;
-          unsigned off = 0;
-          if (act[q]) off = h[d[q]];
-          __syncwarp();
-          if (act[q] && before == 0) h[d[q]] = off + __popc(peers[q]);
-          __syncwarp();
-          if (act[q]) dst[off + __popc(before)] = e[q];
-        }
-      }
-    }
-    __syncwarp();
-    u64* t = src; src = dst; dst = t;
-  }
-  return src;
-}
-
 // In-place bitonic network for rows too long for two buffers; all threads of the CTA, one row.
 // Every compare-exchange moves the smaller key to the lower index, so the virtual +inf elements at
 // positions >= n never move and need no storage.
@@ -362,6 +289,173 @@ __device__ __forceinline__ void bitonic_sort_cta(u64* keys, int n, int tid) {
   }
 }
 
+// ------------------------------------------------------------------------------------------- compact warp sort
+// The warp sort of snn_sort_kernel keeps keys (32-bit sortable value bits) and source indices (16 bit)
+// in separate arrays and packs the four digit histograms two to a word: 12 bytes per input and 2 KB per
+// warp instead of 16 bytes and 4 KB, which lets a third CTA (24 instead of 16 rows) be resident per SM
+// at fan-in 577 -- the kernel is bound by shared-memory latency, so resident rows are what it needs.
+struct SortBuffers {
+  uint32_t* key[2];
+  unsigned short* idx[2];
+  unsigned* hist;   // [0,256): digit 0 in bits 0..15, digit 1 in bits 16..31; [256,512): digits 2 and 3
+};
+__host__ __device__ __forceinline__ size_t sort_bytes_per_warp(int I) {
+  return (((size_t)12 * I + 15) & ~(size_t)15) + 2048;
+}
+__device__ __forceinline__ SortBuffers sort_buffers(unsigned char* base, int I) {
+  SortBuffers b;
+  b.key[0] = reinterpret_cast<uint32_t*>(base);
+  b.key[1] = b.key[0] + I;
+  b.idx[0] = reinterpret_cast<unsigned short*>(b.key[1] + I);
+  b.idx[1] = b.idx[0] + I;
+  b.hist = reinterpret_cast<unsigned*>(base + (((size_t)12 * I + 15) & ~(size_t)15));
+  return b;
+}
+
+// gather as gather_row, into (key[0], idx[0]); counts = false for rows that are ranked with shuffles
+__device__ __forceinline__ int gather_row_compact(const Geometry& g, const float* __restrict__ x, int r, int lane,
+                                                  const SortBuffers& sb, bool counts, const TapCursor& start) {
+  const int I = g.I;
+  const float maxcomp = g.maxv - 0.1f;
+  int n = 0;
+  int h0 = 0, w0 = 0;
+  const float* xr = x + (size_t)r * I;
+  TapCursor cur = start;
+  if (g.is_conv) {
+    const int nw = r % g.Nw;
+    const int t = r / g.Nw;
+    const int nh = t % g.Nh;
+    const int b = t / g.Nh;
+    h0 = nh * g.Sh - g.pad_top;
+    w0 = nw * g.Sw - g.pad_left;
+    xr = x + (size_t)b * g.H * g.W * g.C;
+  }
+  constexpr int kBatch = 4;   // loads in flight per lane before anything depends on them
+  for (int i0 = 0; i0 < I; i0 += 32 * kBatch) {
+    float v[kBatch];
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      const int i = i0 + 32 * q + lane;
+      v[q] = g.maxv;
+      if (i < I) {
+        if (!g.is_conv) {
+          v[q] = __ldg(xr + i);
+        } else {
+          const int h = h0 + cur.kh, ww = w0 + cur.kw;
+          if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v[q] = __ldg(xr + ((size_t)h * g.W + ww) * g.C + cur.c);
+        }
+      }
+      if (g.is_conv) cur.advance32(g);
+    }
+#pragma unroll
+    for (int q = 0; q < kBatch; ++q) {
+      const int i = i0 + 32 * q + lane;
+      const bool keep = (i < I) && !(v[q] > maxcomp);
+      const unsigned mask = __ballot_sync(0xffffffffu, keep);
+      if (keep) {
+        const uint32_t key = float_to_sortable(v[q]);
+        const int pos = n + __popc(mask & ((1u << lane) - 1u));
+        sb.key[0][pos] = key;
+        sb.idx[0][pos] = (unsigned short)i;
+        if (counts) {
+          atomicAdd(&sb.hist[key & 255u], 1u);
+          atomicAdd(&sb.hist[(key >> 8) & 255u], 1u << 16);
+          atomicAdd(&sb.hist[256 + ((key >> 16) & 255u)], 1u);
+          atomicAdd(&sb.hist[256 + (key >> 24)], 1u << 16);
+        }
+      }
+      n += __popc(mask);
+    }
+  }
+  return n;
+}
+
+// n <= 32: rank every (key, index) against the others with shuffles. buffers 0 -> 1, one warp.
+__device__ __forceinline__ void sort_small_compact(const SortBuffers& sb, int n, int lane) {
+  const u64 e = lane < n ? (((u64)sb.key[0][lane] << 32) | sb.idx[0][lane]) : ~0ull;
+  int rank = 0;
+  for (int j = 0; j < n; ++j) {
+    const u64 o = __shfl_sync(0xffffffffu, e, j);
+    rank += o < e;
+  }
+  if (lane < n) { sb.key[1][rank] = (uint32_t)(e >> 32); sb.idx[1][rank] = (unsigned short)e; }
+}
+
+// Stable LSD radix sort, 8 bits per pass, one warp; returns which buffer (0/1) holds the result.
+__device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int n, int lane) {
+  int cur = 0;
+  const unsigned lt = (1u << lane) - 1u;
+#pragma unroll 1
+  for (int p = 0; p < 4; ++p) {
+    unsigned* h = sb.hist + ((p >> 1) << 8);
+    const int fs = (p & 1) << 4;   // this digit's 16-bit field inside the packed word
+    unsigned wds[8], c[8], s = 0;
+    bool single = false;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      wds[q] = h[lane * 8 + q];
+      c[q] = (wds[q] >> fs) & 0xFFFFu;
+      single |= (c[q] == (unsigned)n);
+      s += c[q];
+    }
+    if (__any_sync(0xffffffffu, single)) continue;   // every key has the same digit here: nothing to do
+    unsigned incl = s;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const unsigned o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    unsigned run = incl - s;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {   // the field now holds the bin's running offset (<= n < 65536)
+      h[lane * 8 + q] = (wds[q] & ~(0xFFFFu << fs)) | (run << fs);
+      run += c[q];
+    }
+    __syncwarp();
+    const uint32_t* srcK = sb.key[cur];
+    const unsigned short* srcI = sb.idx[cur];
+    uint32_t* dstK = sb.key[cur ^ 1];
+    unsigned short* dstI = sb.idx[cur ^ 1];
+    const int shift = 8 * p;
+    constexpr int kSB = 4;   // batches of 32 keys whose loads and digit matches go ahead of the serial part
+    for (int i0 = 0; i0 < n; i0 += 32 * kSB) {
+      uint32_t k[kSB];
+      unsigned short ix[kSB];
+      unsigned d[kSB], peers[kSB];
+      bool act[kSB];
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) {
+        const int i = i0 + 32 * q + lane;
+        act[q] = i < n;
+        k[q] = act[q] ? srcK[i] : 0u;
+        ix[q] = act[q] ? srcI[i] : (unsigned short)0;
+        d[q] = act[q] ? (k[q] >> shift) & 255u : 256u + (unsigned)lane;
+      }
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) peers[q] = __match_any_sync(0xffffffffu, d[q]);
+#pragma unroll
+      for (int q = 0; q < kSB; ++q) {
+        if (i0 + 32 * q < n) {   // warp-uniform
+          const unsigned before = peers[q] & lt;
+          unsigned word = 0;
+          if (act[q]) word = h[d[q]];
+          __syncwarp();
+          if (act[q] && before == 0) h[d[q]] = word + ((unsigned)__popc(peers[q]) << fs);
+          __syncwarp();
+          if (act[q]) {
+            const unsigned pos = ((word >> fs) & 0xFFFFu) + __popc(before);
+            dstK[pos] = k[q];
+            dstI[pos] = ix[q];
+          }
+        }
+      }
+    }
+    __syncwarp();
+    cur ^= 1;
+  }
+  return cur;
+}
+
 // ------------------------------------------------------------------------------------------- kernels
 // Sort kernel: one warp per row. Shared memory per warp: two key buffers of I entries and the four
 // digit histograms. Sorted keys go to keys_g[r*istride ..], their count to nvalid_g[r].
@@ -371,29 +465,26 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int I = g.I;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
-  unsigned char* mine = smem_raw + (size_t)warp * (2 * (size_t)I * sizeof(u64) + kHistWords * sizeof(unsigned));
-  u64* a = reinterpret_cast<u64*>(mine);
-  u64* b = a + I;
-  unsigned* hist = reinterpret_cast<unsigned*>(b + I);
+  const SortBuffers sb = sort_buffers(smem_raw + (size_t)warp * sort_bytes_per_warp(I), I);
   TapCursor start = {0, 0, 0};
   if (g.is_conv) start.init(g, lane);
+  const bool tiny = I <= 32;   // ranked with shuffles: no digit histograms needed
   for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
-    const bool tiny = I <= 32;   // ranked with shuffles: no digit histograms needed
     if (!tiny) {
-      for (int q = lane; q < kHistWords; q += 32) hist[q] = 0u;
+      for (int q = lane; q < 512; q += 32) sb.hist[q] = 0u;
       __syncwarp();
     }
-    const int n = gather_row(g, x, r, lane, a, tiny ? nullptr : hist, start);
+    const int n = gather_row_compact(g, x, r, lane, sb, !tiny, start);
     __syncwarp();
-    const u64* res;
-    if (n <= 32) { sort_small(a, b, n, lane); res = b; }
-    else res = radix_sort_row(a, b, n, hist, lane);
+    int res;
+    if (n <= 32) { sort_small_compact(sb, n, lane); res = 1; }
+    else res = radix_sort_row_compact(sb, n, lane);
     __syncwarp();
     WalkEntry* dst = keys_g + (size_t)r * istride;
-    for (int i = lane; i < n; i += 32) {
-      const u64 e = res[i];
-      dst[i] = make_uint2(__float_as_uint(key_value(e)), (uint32_t)e * (uint32_t)g.J);
-    }
+    const uint32_t* rk = sb.key[res];
+    const unsigned short* ri = sb.idx[res];
+    for (int i = lane; i < n; i += 32)
+      dst[i] = make_uint2(__float_as_uint(sortable_to_float(rk[i])), (uint32_t)ri[i] * (uint32_t)g.J);
     if (lane == 0) nvalid_g[r] = n;
     __syncwarp();
   }
@@ -513,8 +604,8 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   };
 
   const size_t budget = (size_t)li.max_smem_optin - 1024;
-  const size_t per_warp = 2 * (size_t)g.I * sizeof(u64) + kHistWords * sizeof(unsigned);
-  if (per_warp > budget) {
+  const size_t per_warp = sort_bytes_per_warp(g.I);
+  if (per_warp > budget || g.I > 65535) {
     // rows too long for the warp sort: one CTA-wide bitonic sort per row, then the walk
     const size_t smem = (size_t)g.I * sizeof(u64);
     if (smem > budget) return E_UNSUPPORTED;
