@@ -146,7 +146,8 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *   snntc_profile_backward_parts  bit 0: run the dX kernel, bit 1: run the dW kernels (default 3);
  *                                 lets a profiler time the two halves of a backward call apart
  *   snntc_profile_forward_parts   bit 0: run the sort kernel, bit 1: run the walk kernel (default 3); with 1 the
- *                                 outputs are not written -- for timing the sort alone
+ *                                 outputs are not written -- for timing the sort alone; bits 2-3, when not 0,
+ *                                 force the walk kernel's outputs per lane (1: fewest ... 3: most)
  *   snntc_set_overlap             1 (default): the two independent kernels of a backward call (dX, dW) run side
  *                                 by side, dX on one library-owned auxiliary stream per device that is joined
  *                                 back with events, so the caller still sees plain stream order; 0: everything

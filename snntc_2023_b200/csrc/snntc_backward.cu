@@ -42,6 +42,27 @@ __device__ __forceinline__ void masked_fma(float& acc, float x, float y, float u
       : "+f"(acc) : "f"(x), "f"(y), "f"(u), "f"(w));
 }
 
+// Two-lane FP32 arithmetic of sm_100 (one issue slot for two IEEE single-precision results; each lane
+// rounds exactly like the scalar instruction). A pair lives in one 64-bit register: low word = lane 0.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // ------------------------------------------------------------------------------------------- dX
 // "Points" p are dense samples (taps = 1, CH = I) or input pixels (taps = Kh*Kw, CH = C). The
 // reduction runs over tiles t = (tap, block of 16 outputs); the loads of tile t+1 are issued before
@@ -382,9 +403,11 @@ template <bool VEC>   // VEC: J % 4 == 0, the y/u tiles are fetched with 16-byte
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
+  // y and u are kept as (-y,-y) and (u,u) pairs so that the packed two-lane FP32 instructions below
+  // can take them as 64-bit operands without a register move
   __shared__ __align__(16) float Xs[2][kRT * kTileI];
-  __shared__ __align__(16) float Ys[2][kRT * kTile];
-  __shared__ __align__(16) float Us[2][kRT * kTile];
+  __shared__ __align__(16) float2 NYs[2][kRT * kTile];
+  __shared__ __align__(16) float2 Us[2][kRT * kTile];
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
@@ -474,22 +497,30 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 #pragma unroll
     for (int q = 0; q < kRT / 2; ++q) Xs[buf][(lx_r + 2 * q) * kTileI + lx_c] = px[q];
     if (VEC) {
-      *reinterpret_cast<float4*>(&Ys[buf][ly_r * kTile + ly_c]) = make_float4(py[0], py[1], py[2], py[3]);
-      *reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + ly_c]) = make_float4(pu[0], pu[1], pu[2], pu[3]);
+      // columns 4t, 4t+1 of the 16 column groups t sit side by side in the first half of a row of pairs,
+      // columns 4t+2, 4t+3 in the second half: the 16-byte reads of 8 neighbouring threads are then contiguous
+      float4* ny = reinterpret_cast<float4*>(&NYs[buf][ly_r * kTile + (ly_c >> 1)]);
+      float4* uu = reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + (ly_c >> 1)]);
+      ny[0] = make_float4(-py[0], -py[0], -py[1], -py[1]);
+      ny[kTile / 4] = make_float4(-py[2], -py[2], -py[3], -py[3]);
+      uu[0] = make_float4(pu[0], pu[0], pu[1], pu[1]);
+      uu[kTile / 4] = make_float4(pu[2], pu[2], pu[3], pu[3]);
     } else {
+      const int slot = ((ly_c >> 1) & 1) * (kTile / 2) + 2 * (ly_c >> 2) + (ly_c & 1);
 #pragma unroll
       for (int q = 0; q < kRT / 4; ++q) {
-        Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q];
-        Us[buf][(ly_r + 4 * q) * kTile + ly_c] = pu[q];
+        NYs[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(-py[q], -py[q]);
+        Us[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(pu[q], pu[q]);
       }
     }
   };
 
-  float acc[8][4];
+  // acc[a2][b] holds the sums of fan-in rows (8*ti + 2*a2, +1) and output column 4*tj + b as one 64-bit pair
+  uint64_t acc[4][4];
 #pragma unroll
-  for (int a = 0; a < 8; ++a)
+  for (int a = 0; a < 4; ++a)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+    for (int b = 0; b < 4; ++b) acc[a][b] = pack2(0.f, 0.f);
 
   if (r_begin < r_end) {
     fetch(r_begin);
@@ -505,20 +536,24 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 
 #pragma unroll
     for (int rr = 0; rr < kRT; ++rr) {
-      const float4 xa4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti]);
-      const float4 xb4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
-      const float4 y4 = *reinterpret_cast<const float4*>(&Ys[buf][rr * kTile + 4 * tj]);
-      const float4 u4 = *reinterpret_cast<const float4*>(&Us[buf][rr * kTile + 4 * tj]);
-      const float xa[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
-      const float ya[4] = {y4.x, y4.y, y4.z, y4.w};
-      const float ua[4] = {u4.x, u4.y, u4.z, u4.w};
+      const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(&Xs[buf][rr * kTileI + 8 * ti]);
+      const ulonglong2 xb = *reinterpret_cast<const ulonglong2*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
+      const ulonglong2 ya = *reinterpret_cast<const ulonglong2*>(&NYs[buf][rr * kTile + 2 * tj]);
+      const ulonglong2 yb = *reinterpret_cast<const ulonglong2*>(&NYs[buf][rr * kTile + kTile / 2 + 2 * tj]);
+      const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + 2 * tj]);
+      const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + kTile / 2 + 2 * tj]);
+      const uint64_t x2[4] = {xa.x, xa.y, xb.x, xb.y};
+      const uint64_t ny2[4] = {ya.x, ya.y, yb.x, yb.y};
+      const uint64_t u2[4] = {ua.x, ua.y, ub.x, ub.y};
 #pragma unroll
-      for (int a = 0; a < 8; ++a)
+      for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          // [x<=y]*(x-y) == min(x,y)-y, bit for bit, and is 0 for sentinel inputs (x > every fired y)
-          const float d = fminf(xa[a], ya[b]) - ya[b];
-          acc[a][b] = fmaf(d, ua[b], acc[a][b]);
+          // [x<=y]*(x-y) == min(x-y, 0), bit for bit (x-y of distinct floats never rounds to zero), and is 0
+          // for sentinel inputs (x > every fired y); two fan-in rows per packed add / packed fma
+          float lo, hi;
+          unpack2(add2(x2[a], ny2[b]), lo, hi);
+          acc[a][b] = fma2(pack2(fminf(lo, 0.f), fminf(hi, 0.f)), u2[b], acc[a][b]);
         }
     }
 
@@ -528,11 +563,14 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 
   float* __restrict__ dst = partial + (size_t)blockIdx.z * Itot * J;
 #pragma unroll
-  for (int a = 0; a < 8; ++a)
+  for (int a = 0; a < 4; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
-      const int i = i0 + 8 * ti + a, j = j0 + 4 * tj + b;
-      if (i < Itot && j < J) dst[(size_t)i * J + j] = acc[a][b];
+      float lo, hi;
+      unpack2(acc[a][b], lo, hi);
+      const int i = i0 + 8 * ti + 2 * a, j = j0 + 4 * tj + b;
+      if (i < Itot && j < J) dst[(size_t)i * J + j] = lo;
+      if (i + 1 < Itot && j < J) dst[(size_t)(i + 1) * J + j] = hi;
     }
 }
 

@@ -24,6 +24,11 @@ namespace {
 
 constexpr int kFwdThreads = 256;
 constexpr int kFwdWarps = kFwdThreads / 32;
+// packed walk: instructions per warp-step and resident CTAs per SM for 1 / 2 / 4 output pairs per lane, and the
+// widest fan-out that still uses 2 pairs per lane
+constexpr double kWalk2Cost[3] = {12.0, 17.0, 27.0};
+constexpr int kWalk2Ctas[3] = {4, 3, 2};
+constexpr int kWalk2TopJ = 1 << 30;
 
 typedef unsigned long long u64;
 
@@ -177,6 +182,169 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       const int j = jbase + lane + 32 * m;
       y_row[j] = yv;
       inv_row[j] = iv;
+    }
+  }
+}
+
+// ---- two outputs per 64-bit register ---------------------------------------------------------------
+// sm_100 has two-lane FP32 add / sub / fma on 64-bit register pairs: one issue slot, two results, each
+// rounded exactly like the scalar instruction. A pair holds outputs (j, j+1) of one lane.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ void unpack2i(uint64_t v, int& lo, int& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// walk_row with the outputs of a lane held as JP pairs (j, j+1), j = jbase + 2*lane + 64*m: the three
+// FP32 operations of a step (q, the weight sum, the weighted sum) are one packed instruction per pair and
+// a weight-row read is one 8-byte load per pair. The weight sum is carried NEGATED (nws = theta - sum w), so
+// that q = fma(x, nws, ysum) needs no negated copy of x; negation is exact, so every value is bit for bit the
+// scalar walk's -- except the sign of an exactly cancelled sum (+0 on both sides), which is why the sum is
+// read back as 0 - nws: 1/(+0) = +inf clamps to "no spike", 1/(-0) would not. Requires J even and the
+// weights 8-byte aligned.
+template <int JP, int CH, bool FULL>
+__device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
+                                          const float* __restrict__ w, int jbase, int lane,
+                                          float* __restrict__ y_row, float* __restrict__ inv_row) {
+  const int J = g.J;
+  int jl[JP];
+  bool jok[JP];
+  uint64_t nws[JP], ys[JP];
+  float wfin[2 * JP], yfin[2 * JP];
+  int live[2 * JP];
+#pragma unroll
+  for (int m = 0; m < JP; ++m) {
+    const int j = jbase + 2 * lane + 64 * m;
+    jok[m] = FULL || j < J;
+    jl[m] = jok[m] ? j : J - 2;
+    float n0 = g.theta, n1 = g.theta, y0 = 0.f, y1 = 0.f;
+    if (g.has_bias) {  // the bias input (value biasvolt, weight row I) is always consumed first
+      const float2 wb = __ldg(reinterpret_cast<const float2*>(w + (size_t)g.I * J + jl[m]));
+      n0 -= wb.x; n1 -= wb.y;
+      y0 = g.biasvolt * wb.x; y1 = g.biasvolt * wb.y;
+    }
+    nws[m] = pack2(n0, n1);
+    ys[m] = pack2(y0, y1);
+    wfin[2 * m] = 0.f - n0; wfin[2 * m + 1] = 0.f - n1;
+    yfin[2 * m] = y0; yfin[2 * m + 1] = y1;
+    live[2 * m] = live[2 * m + 1] = -1;
+  }
+  float xprev = g.has_bias ? g.biasvolt : 0.f;
+
+  const float* wl = w + (FULL ? jbase + 2 * lane : 0);
+
+  auto step = [&](const float x, const uint64_t (&wv)[JP]) {
+    const uint64_t x2 = pack2(x, x);
+    int q[2 * JP];
+#pragma unroll
+    for (int m = 0; m < JP; ++m) unpack2i(fma2(x2, nws[m], ys[m]), q[2 * m], q[2 * m + 1]);
+    int orall = q[0] | q[1];
+    if (JP == 2) orall = or3(orall, q[2], q[3]);
+    if (JP == 4) orall = or3(or3(orall, q[2], q[3]), or3(q[4], q[5], q[6]), q[7]);
+    if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
+      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive
+#pragma unroll
+      for (int m = 0; m < JP; ++m) {
+        float n[2], y[2];
+        unpack2(nws[m], n[0], n[1]);
+        unpack2(ys[m], y[0], y[1]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float wsum = 0.f - n[h];   // not -n: an exactly cancelled sum must read +0 as in the scalar walk
+          const bool fire = (q[2 * m + h] < 0) & (live[2 * m + h] != 0) & ratio_gt(y[h], wsum, xprev) & ratio_le(y[h], wsum, x);
+          if (fire) {
+            live[2 * m + h] = 0;   // spike lies in (previous input, x]: keep the sums aside ...
+            wfin[2 * m + h] = wsum;
+            yfin[2 * m + h] = y[h];
+            n[h] = CUDART_INF_F;   // ... and park the running weight sum where q stays +inf
+          }
+        }
+        nws[m] = pack2(n[0], n[1]);
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < JP; ++m) {
+      nws[m] = sub2(nws[m], wv[m]);
+      ys[m] = fma2(x2, wv[m], ys[m]);
+    }
+    xprev = x;
+  };
+  auto load_pair = [&](const float* wrow, int m) -> uint64_t {
+    return __ldg(reinterpret_cast<const unsigned long long*>(FULL ? wrow + 64 * m : wrow + jl[m]));
+  };
+
+  int k = 0;
+  bool all_done = false;
+  for (; k + CH <= nvalid && !all_done; k += CH) {
+    float xs[CH];
+    uint64_t wv[CH][JP];
+#pragma unroll
+    for (int u = 0; u < CH; ++u) {
+      const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
+      xs[u] = __uint_as_float(e.x);
+      const float* wrow = wl + e.y;
+#pragma unroll
+      for (int m = 0; m < JP; ++m) wv[u][m] = load_pair(wrow, m);
+    }
+#pragma unroll
+    for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
+    int any_live = 0;
+#pragma unroll
+    for (int m = 0; m < 2 * JP; ++m) any_live |= live[m];
+    all_done = !__any_sync(0xffffffffu, any_live != 0);
+  }
+  if (!all_done) {
+    for (; k < nvalid; ++k) {
+      const WalkEntry e = __ldcg(ents + k);
+      const float* wrow = wl + e.y;
+      uint64_t wv[JP];
+#pragma unroll
+      for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
+      step(__uint_as_float(e.x), wv);
+    }
+  }
+
+#pragma unroll
+  for (int m = 0; m < JP; ++m) {
+    float n[2], y[2];
+    unpack2(nws[m], n[0], n[1]);
+    unpack2(ys[m], y[0], y[1]);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      // an output that stopped has fired; one that consumed every input fires iff it is armed
+      bool fired = true;
+      float ws = wfin[2 * m + h], yy = yfin[2 * m + h];
+      if (live[2 * m + h]) {
+        ws = 0.f - n[h]; yy = y[h];
+        fired = ratio_gt(yy, ws, xprev);
+      }
+      float yv = g.maxv, iv = 0.f;
+      if (fired) {
+        iv = __fdividef(1.0f, ws);
+        yv = yy * iv;
+        if (yv >= g.maxv) { yv = g.maxv; iv = 0.f; }
+      }
+      if (jok[m]) {
+        const int j = jbase + 2 * lane + 64 * m + h;
+        y_row[j] = yv;
+        inv_row[j] = iv;
+      }
     }
   }
 }
@@ -543,6 +711,31 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
   }
 }
 
+// The same items with the outputs of a lane held in pairs (walk_row2): a warp covers 64*JP outputs.
+template <int JP>
+__global__ void __launch_bounds__(kFwdThreads)
+snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
+                 const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
+  const int J = g.J, R = g.R;
+  const int lane = threadIdx.x & 31;
+  const int jchunks = (J + 64 * JP - 1) / (64 * JP);
+  const bool full_j = (J % (64 * JP)) == 0;
+  float* __restrict__ y_out = out;
+  float* __restrict__ inv_out = out + (size_t)R * J;
+  const long items = (long)(row_end - row_begin) * jchunks;
+  const long wstride = (long)gridDim.x * kFwdWarps;
+  for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
+    const int rl = (int)(item / jchunks), jc = (int)(item - (long)rl * jchunks);
+    const int r = row_begin + rl;
+    const WalkEntry* krow = keys_g + (size_t)r * istride;
+    const int n = __ldg(nvalid_g + r);
+    if (full_j)
+      walk_row2<JP, (JP >= 2 ? 4 : 8), true>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+    else
+      walk_row2<JP, (JP >= 2 ? 4 : 8), false>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+  }
+}
+
 int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of keys start 16-byte aligned
 
 size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
@@ -556,6 +749,19 @@ int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g,
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
   snn_walk_kernel<JPT><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
+}
+
+template <int JP>
+int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
+                 const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end) {
+  const int jchunks = (g.J + 64 * JP - 1) / (64 * JP);
+  const long items = (long)(row_end - row_begin) * jchunks;
+  long grid = (items + kFwdWarps - 1) / kFwdWarps;
+  const long cap = (long)li.num_sms * 8;
+  if (grid > cap) grid = cap;
+  snn_walk2_kernel<JP><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -574,32 +780,47 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   const int istride = key_stride(g);
 
   const int fparts = forward_parts();
-  // Outputs per lane (JPT): more of them amortise the per-step cost (list entry, address, vote) over more
-  // outputs, fewer give more (row, output block) items to spread over the SMs. Measured instructions per
-  // warp-step are about 19 / 24 / 39 for JPT 1 / 2 / 4 and 6 / 4 / 3 CTAs fit per SM; pick the smallest
+  // Outputs per lane: more of them amortise the per-step cost (list entry, address, vote) over more
+  // outputs, fewer give more (row, output block) items to spread over the SMs. `cost` is the measured number
+  // of instructions per warp-step, `ctas` how many CTAs fit per SM; with few items pick the smallest
   // estimate of (waves of items) x (cost of a step).
-  int jpt = g.J <= 32 ? 1 : (g.J <= 64 ? 2 : 4);   // many items: most outputs per lane the row can fill
-  {
-    const double cost[3] = {19.0, 24.0, 39.0};
-    const int ctas[3] = {6, 4, 3};
-    const int top = jpt == 1 ? 0 : (jpt == 2 ? 1 : 2);
-    const double items_top = (double)g.R * ((g.J + 32 * jpt - 1) / (32 * jpt));
+  auto pick = [&](int unit, const double (&cost)[3], const int (&ctas)[3], int top) {
+    int best_c = top;
+    const double items_top = (double)g.R * ((g.J + unit * (1 << top) - 1) / (unit * (1 << top)));
     if (items_top < 4.0 * li.num_sms * ctas[top] * kFwdWarps) {
-      // few items: whole waves of items matter, pick the smallest (waves) x (cost of a step)
       double best = 0;
       for (int c = 0; c <= top; ++c) {
-        const int cand = 1 << c;
-        const double items = (double)g.R * ((g.J + 32 * cand - 1) / (32 * cand));
+        const int per = unit * (1 << c);
+        const double items = (double)g.R * ((g.J + per - 1) / per);
         const double slots = (double)li.num_sms * ctas[c] * kFwdWarps;
         const double est = (double)(long)(items / slots + 0.999) * cost[c];
-        if (c == 0 || est < best) { best = est; jpt = cand; }
+        if (c == 0 || est < best) { best = est; best_c = c; }
       }
     }
+    return best_c;
+  };
+  // packed walk (two outputs per 64-bit register) whenever the output pairs are 8-byte aligned
+  const bool pairs = (g.J % 2 == 0) && (reinterpret_cast<uintptr_t>(w) % 8 == 0);
+  int jsel;
+  if (pairs) {
+    const double cost[3] = {kWalk2Cost[0], kWalk2Cost[1], kWalk2Cost[2]};
+    const int ctas[3] = {kWalk2Ctas[0], kWalk2Ctas[1], kWalk2Ctas[2]};
+    jsel = pick(64, cost, ctas, g.J <= 64 ? 0 : (g.J <= kWalk2TopJ ? 1 : 2));
+  } else {
+    const double cost[3] = {19.0, 24.0, 39.0};
+    const int ctas[3] = {6, 4, 3};
+    jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
   }
+  if (((fparts >> 2) & 3) != 0) jsel = ((fparts >> 2) & 3) - 1;   // measurement aid: force the outputs per lane
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (jpt == 1) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    if (jpt == 2) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (pairs) {
+      if (jsel == 0) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      if (jsel == 1) return launch_walk2<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      return launch_walk2<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    }
+    if (jsel == 0) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (jsel == 1) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
   };
 

@@ -28,6 +28,7 @@ class Profile:
     recorded on the calling stream; used by bench.py to time the kernels of a step one by one."""
     records = None
     split_forward = False   # also time each forward call's sort kernel alone (tag "<op>_forward_sort")
+    forward_bits = 0        # extra bits for snntc_profile_forward_parts while split_forward toggles it
 
     @staticmethod
     def begin(t):
@@ -112,12 +113,12 @@ def snn_fc(inp, weight, params):
         out = torch.empty((2 * B, J), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
         if Profile.records is not None and Profile.split_forward:
-            lib.snntc_profile_forward_parts(1)
+            lib.snntc_profile_forward_parts(1 | Profile.forward_bits)
             ev = Profile.begin(x)
             lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
                                  _ptr(ws), wsb, _stream(x))
             Profile.end(ev, x, "fc_forward_sort", (B, rows, J))
-            lib.snntc_profile_forward_parts(3)
+            lib.snntc_profile_forward_parts(3 | Profile.forward_bits)
         ev = Profile.begin(x)
         rc = lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
                                   _ptr(ws), wsb, _stream(x))
@@ -175,12 +176,12 @@ def snn_cv(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
         out = torch.empty((2 * B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
         if Profile.records is not None and Profile.split_forward:
-            lib.snntc_profile_forward_parts(1)
+            lib.snntc_profile_forward_parts(1 | Profile.forward_bits)
             ev = Profile.begin(x)
             lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
                                  pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
             Profile.end(ev, x, "cv_forward_sort", (B * Nh * Nw, rows, Kc))
-            lib.snntc_profile_forward_parts(3)
+            lib.snntc_profile_forward_parts(3 | Profile.forward_bits)
         ev = Profile.begin(x)
         rc = lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
                                   pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))

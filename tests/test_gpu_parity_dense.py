@@ -88,6 +88,29 @@ def test_dense_sentinel_inputs():
     assert np.all(dx.cpu().numpy()[:, ::3] == 0)
 
 
+@pytest.mark.parametrize("J", [1, 2, 10, 64, 128, 256])
+@pytest.mark.parametrize("bv", [0.0, 1.0])
+def test_dense_weight_sum_cancels_exactly(J, bv):
+    """sum(w) - theta == +0 after the last input with a positive weighted sum: the reference takes 1/0 = +inf,
+    so the spike value is +inf >= MAX and the output reads "no spike" (MAX, 0) (snnfc_kernels.cu.cc:60-68).
+    Every way the walk carries its sums (scalar, pairs, negated) has to land on the same side of zero."""
+    import torch
+    from snntc_2023_b200 import ops
+    x = np.array([[1.5, 2.0], [2.0, 1.5], [1.25, 1.75]], np.float32)
+    rows = [[0.25] * J, [0.5] * J] + ([[0.25] * J] if bv > 0 else [])   # bias row last
+    if bv == 0:
+        rows = [[0.5] * J, [0.5] * J]
+    w = np.array(rows, np.float32)
+    w[:, J // 2:] += np.float32(0.125) * (J > 1)    # other half: an ordinary finite spike beside the cancelled one
+    params = O.fc_params(biasvolt=bv)
+    out = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params).cpu().numpy()
+    ref = O.fc_forward(x, w, params, "f32")
+    assert np.array_equal(out[:3], ref["y"]) and np.array_equal(out[3:], ref["inv"])
+    ncancel = J // 2 if J > 1 else 1
+    assert np.all(out[:3, :ncancel] == 1e5) and np.all(out[3:, :ncancel] == 0)
+    assert np.all(np.isfinite(out))
+
+
 def test_dense_repeatable():
     """No atomics on the dense path: two runs give identical bits."""
     import torch
