@@ -13,6 +13,8 @@
 #include "snntc_common.cuh"
 
 #include <math_constants.h>
+#include <math.h>
+#include <type_traits>
 
 namespace snntc {
 
@@ -27,13 +29,31 @@ constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs,
 
 // u[r,j] = fired ? grad[r,j] * inv[r,j] : 0, once per backward call (the reference does the same with an
 // Eigen expression, snnfcgrad_kernels.cu.cc:156-173); both gradient kernels then read (y, u).
+// Besides u, this kernel decides whether the dW kernel may use its scaled, saturating inner loop (see
+// snn_dw_kernel): *exact_flag is raised when some value lies outside the range in which scaling by a power
+// of two is exact and (y - x) * scale stays below 1 -- an input below -MAX, a non-zero input or spike value
+// smaller than 2^-60 in magnitude, or a u that is not below 2^100 in magnitude (NaN and inf included).
+// `xin` is the whole input tensor (nx elements). The flag must be zero before the launch.
 __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
-                             size_t n, float maxcomp) {
+                             size_t n, float maxcomp, const float* __restrict__ xin, size_t nx, float maxv,
+                             int* __restrict__ exact_flag) {
+  const float tiny = 8.67361737988e-19f;   // 2^-60
+  const float big = 1.26765060023e30f;     // 2^100
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  bool odd = false;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
     const float y = __ldg(out + e);
-    u[e] = (y > maxcomp) ? 0.f : __ldg(grad + e) * __ldg(out + n + e);
+    const float uu = (y > maxcomp) ? 0.f : __ldg(grad + e) * __ldg(out + n + e);
+    u[e] = uu;
+    const float ya = fabsf(y);
+    odd |= (ya > 0.f && ya < tiny) || !(fabsf(uu) < big);
   }
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < nx; e += stride) {
+    const float xv = __ldg(xin + e);
+    const float xa = fabsf(xv);
+    odd |= (xv < -maxv) || (xa > 0.f && xa < tiny);
+  }
+  if (odd) *exact_flag = 1;
 }
 
 // acc += [x <= y] * u * w as one compare and one predicated FMA
@@ -51,11 +71,6 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
 }
 __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
@@ -399,19 +414,39 @@ snn_dx_wide_kernel(const Geometry g, const float* __restrict__ uv, const float* 
 // selects a slice of the rows r. partial = dw when gridDim.z == 1, else the slice's own [Itot,J] plane
 // of the workspace. Same software pipeline as dX: the next 16 rows are loaded into registers while the
 // current 16 are being reduced out of (double-buffered) shared memory.
+//
+// Per element the sum takes [x<=y]*(x-y)*u = relu(y-x)*(-u). With s a power of two such that (y-x)*s < 1
+// for every pair that can occur, relu((y-x)*s) is ONE saturating add of the pre-scaled tiles, y*s + (-x*s)
+// clamped to [0,1], and the product with -u/s is the same real number as before, so the fused multiply-add
+// rounds to the same bits: one FADD.SAT per element plus one two-lane FMA per two elements, nothing on the
+// half-rate compare/min pipe. Scaling by s is exact unless it underflows, and the bound on (y-x) needs
+// x >= -MAX; snn_u_kernel checks the ranges of the call's tensors and raises *exact_flag otherwise, in
+// which case the tiles stay unscaled (s = 1) and the clamp is an explicit max(., 0).
+__device__ __forceinline__ float add_sat(float a, float b) {
+  float r;
+  asm("add.rn.sat.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
 template <bool VEC>   // VEC: J % 4 == 0, the y/u tiles are fetched with 16-byte loads
 __global__ void __launch_bounds__(kBwdThreads)
 snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
-              const float* __restrict__ out, float* __restrict__ partial, int rows_per_split) {
-  // y and u are kept as (-y,-y) and (u,u) pairs so that the packed two-lane FP32 instructions below
-  // can take them as 64-bit operands without a register move
+              const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
+              float scale, const int* __restrict__ exact_flag) {
+  // -x*s and y*s as plain tiles; -u/s as (v,v) pairs so that the two-lane FMA takes it as one 64-bit operand:
+  // columns 4t, 4t+1 of the 16 column groups t sit side by side in the first half of a row of pairs,
+  // columns 4t+2, 4t+3 in the second half, so the 16-byte reads of 8 neighbouring threads are contiguous
   __shared__ __align__(16) float Xs[2][kRT * kTileI];
-  __shared__ __align__(16) float2 NYs[2][kRT * kTile];
+  __shared__ __align__(16) float Ys[2][kRT * kTile];
   __shared__ __align__(16) float2 Us[2][kRT * kTile];
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
   const float* __restrict__ yv = out;
+  const bool fast = scale != 1.0f && __ldg(exact_flag) == 0;
+  const float sc = fast ? scale : 1.0f;     // s
+  const float nsc = -sc;                    // -s
+  const float nusc = fast ? -1.0f / scale : -1.0f;   // -1/s, exact: s is a power of two
 
   const int tid = threadIdx.x;
   const int ti = tid >> 4, tj = tid & 15;
@@ -451,7 +486,7 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 #pragma unroll
     for (int q = 0; q < kRT / 2; ++q) {
       const int r = rb + lx_r + 2 * q;
-      // padding of the tile: x=+inf, y=0, u=0 gives min(x,y)-y = 0 and a zero product (never inf-inf)
+      // padding of the tile: x=+inf, y=0, u=0 gives relu(y-x) = 0 and a zero product (never inf-inf)
       float xv = CUDART_INF_F;
       if (r < r_end) {
         if (li < I) {
@@ -495,22 +530,21 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
   };
   auto park = [&](int buf) {
 #pragma unroll
-    for (int q = 0; q < kRT / 2; ++q) Xs[buf][(lx_r + 2 * q) * kTileI + lx_c] = px[q];
+    for (int q = 0; q < kRT / 2; ++q) Xs[buf][(lx_r + 2 * q) * kTileI + lx_c] = px[q] * nsc;
     if (VEC) {
-      // columns 4t, 4t+1 of the 16 column groups t sit side by side in the first half of a row of pairs,
-      // columns 4t+2, 4t+3 in the second half: the 16-byte reads of 8 neighbouring threads are then contiguous
-      float4* ny = reinterpret_cast<float4*>(&NYs[buf][ly_r * kTile + (ly_c >> 1)]);
+      *reinterpret_cast<float4*>(&Ys[buf][ly_r * kTile + ly_c]) =
+          make_float4(py[0] * sc, py[1] * sc, py[2] * sc, py[3] * sc);
       float4* uu = reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + (ly_c >> 1)]);
-      ny[0] = make_float4(-py[0], -py[0], -py[1], -py[1]);
-      ny[kTile / 4] = make_float4(-py[2], -py[2], -py[3], -py[3]);
-      uu[0] = make_float4(pu[0], pu[0], pu[1], pu[1]);
-      uu[kTile / 4] = make_float4(pu[2], pu[2], pu[3], pu[3]);
+      const float u0 = pu[0] * nusc, u1 = pu[1] * nusc, u2 = pu[2] * nusc, u3 = pu[3] * nusc;
+      uu[0] = make_float4(u0, u0, u1, u1);
+      uu[kTile / 4] = make_float4(u2, u2, u3, u3);
     } else {
       const int slot = ((ly_c >> 1) & 1) * (kTile / 2) + 2 * (ly_c >> 2) + (ly_c & 1);
 #pragma unroll
       for (int q = 0; q < kRT / 4; ++q) {
-        NYs[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(-py[q], -py[q]);
-        Us[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(pu[q], pu[q]);
+        Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q] * sc;
+        const float uq = pu[q] * nusc;
+        Us[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(uq, uq);
       }
     }
   };
@@ -521,6 +555,36 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
   for (int a = 0; a < 4; ++a)
 #pragma unroll
     for (int b = 0; b < 4; ++b) acc[a][b] = pack2(0.f, 0.f);
+
+  // 16 rows out of shared memory; FAST: the clamp is the saturation of the add
+  auto reduce_tile = [&](int buf, auto fast_c) {
+    constexpr bool FAST = decltype(fast_c)::value;
+#pragma unroll
+    for (int rr = 0; rr < kRT; ++rr) {
+      const float4 xa4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti]);
+      const float4 xb4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
+      const float4 y4 = *reinterpret_cast<const float4*>(&Ys[buf][rr * kTile + 4 * tj]);
+      const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + 2 * tj]);
+      const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + kTile / 2 + 2 * tj]);
+      const float nx[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
+      const float ys[4] = {y4.x, y4.y, y4.z, y4.w};
+      const uint64_t nu2[4] = {ua.x, ua.y, ub.x, ub.y};
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          float t0, t1;
+          if (FAST) {
+            t0 = add_sat(ys[b], nx[2 * a]);
+            t1 = add_sat(ys[b], nx[2 * a + 1]);
+          } else {
+            t0 = fmaxf(ys[b] + nx[2 * a], 0.f);
+            t1 = fmaxf(ys[b] + nx[2 * a + 1], 0.f);
+          }
+          acc[a][b] = fma2(pack2(t0, t1), nu2[b], acc[a][b]);
+        }
+    }
+  };
 
   if (r_begin < r_end) {
     fetch(r_begin);
@@ -533,30 +597,8 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     const int buf = it & 1;
     const bool more = rb + kRT < r_end;
     if (more) fetch(rb + kRT);
-
-#pragma unroll
-    for (int rr = 0; rr < kRT; ++rr) {
-      const ulonglong2 xa = *reinterpret_cast<const ulonglong2*>(&Xs[buf][rr * kTileI + 8 * ti]);
-      const ulonglong2 xb = *reinterpret_cast<const ulonglong2*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
-      const ulonglong2 ya = *reinterpret_cast<const ulonglong2*>(&NYs[buf][rr * kTile + 2 * tj]);
-      const ulonglong2 yb = *reinterpret_cast<const ulonglong2*>(&NYs[buf][rr * kTile + kTile / 2 + 2 * tj]);
-      const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + 2 * tj]);
-      const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + kTile / 2 + 2 * tj]);
-      const uint64_t x2[4] = {xa.x, xa.y, xb.x, xb.y};
-      const uint64_t ny2[4] = {ya.x, ya.y, yb.x, yb.y};
-      const uint64_t u2[4] = {ua.x, ua.y, ub.x, ub.y};
-#pragma unroll
-      for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          // [x<=y]*(x-y) == min(x-y, 0), bit for bit (x-y of distinct floats never rounds to zero), and is 0
-          // for sentinel inputs (x > every fired y); two fan-in rows per packed add / packed fma
-          float lo, hi;
-          unpack2(add2(x2[a], ny2[b]), lo, hi);
-          acc[a][b] = fma2(pack2(fminf(lo, 0.f), fminf(hi, 0.f)), u2[b], acc[a][b]);
-        }
-    }
-
+    if (fast) reduce_tile(buf, std::true_type{});
+    else reduce_tile(buf, std::false_type{});
     if (more) park(buf ^ 1);
     __syncthreads();
   }
@@ -603,13 +645,28 @@ DwPlan plan_dw(const Geometry& g, const LaunchInfo& li) {
 
 }  // namespace
 
-// workspace = u[R,J] (rounded up to 256 bytes) followed by the partial dW planes (none when splits == 1)
+// workspace = u[R,J] (rounded up to 256 bytes), 256 bytes holding the range flag of snn_u_kernel, then the
+// partial dW planes (none when splits == 1)
 static size_t u_bytes(const Geometry& g) { return (((size_t)g.R * g.J * sizeof(float)) + 255) & ~(size_t)255; }
+constexpr size_t kFlagBytes = 256;
+
+// The power of two s with 2*MAX*s <= 1/2 (so that (y - x)*s < 1 whenever y <= MAX and x >= -MAX), or 1 when
+// MAX or the bias input are outside the range in which the scaled inner loop of snn_dw_kernel is exact.
+static float dw_scale(const Geometry& g) {
+  if (!(g.maxv > 0.f) || !(g.maxv < 1e27f)) return 1.0f;
+  if (g.has_bias) {
+    const float ba = fabsf(g.biasvolt);
+    if (g.biasvolt < -g.maxv || (ba > 0.f && ba < 8.67361737988e-19f)) return 1.0f;
+  }
+  int e = 0;
+  frexpf(g.maxv, &e);            // maxv = m * 2^e, m in [0.5, 1)  =>  maxv < 2^e
+  return ldexpf(1.0f, -(e + 2));  // 2*maxv*s < 2^(e+1) * 2^-(e+2) = 1/2
+}
 
 size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
   const DwPlan p = plan_dw(g, li);
   const size_t part = p.splits <= 1 ? 0 : (size_t)p.splits * (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
-  return u_bytes(g) + part;
+  return u_bytes(g) + kFlagBytes + part;
 }
 
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
@@ -618,6 +675,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   const int parts = backward_parts();
   if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return -5;
   float* uv = static_cast<float*>(ws);
+  int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + u_bytes(g));
   // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
   const bool vec = (g.J % 4 == 0) && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)uv) & 15) == 0 &&
                    (((size_t)g.R * g.J) % 4 == 0);
@@ -625,7 +683,9 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const size_t n = (size_t)g.R * g.J;
     size_t blocks = (n + 255) / 256;
     if (blocks > (size_t)li.num_sms * 8) blocks = (size_t)li.num_sms * 8;
-    snn_u_kernel<<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f);
+    if (cudaMemsetAsync(exact_flag, 0, sizeof(int), s) != cudaSuccess) return E_CUDA;
+    const size_t nx = g.is_conv ? (size_t)g.B * g.H * g.W * g.C : (size_t)g.R * g.I;
+    snn_u_kernel<<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
@@ -656,10 +716,11 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   if (!(parts & 2)) return OK;
   const DwPlan p = plan_dw(g, li);
   float* partial = dw;
-  if (p.splits > 1) partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g));
+  if (p.splits > 1) partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + kFlagBytes);
   dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTileI - 1) / kTileI, p.splits);
-  if (vec) snn_dw_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
-  else snn_dw_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split);
+  const float scale = dw_scale(g);
+  if (vec) snn_dw_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
+  else snn_dw_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   if (p.splits > 1) {

@@ -53,7 +53,7 @@ def test_validation_status_codes_without_a_device():
     for code in range(0, -9, -1):
         assert len(lib.snntc_status_string(code)) > 1
     assert lib.snntc_fc_forward_workspace_bytes(256, 784, 400) >= 256 * 784 * 8
-    assert lib.snntc_fc_backward_workspace_bytes(1, 25088, 25089, 1024) == 4096   # u[1,1024] only: enough tiles, no row split
+    assert lib.snntc_fc_backward_workspace_bytes(1, 25088, 25089, 1024) == 4096 + 256   # u[1,1024] and the range flag: enough tiles, no row split
 
 
 def test_no_cpu_fallback():

@@ -111,6 +111,32 @@ def test_dense_weight_sum_cancels_exactly(J, bv):
     assert np.all(np.isfinite(out))
 
 
+@pytest.mark.parametrize("odd", ["below_minus_max", "tiny", "huge_grad"])
+def test_dense_backward_values_outside_the_scaled_range(odd):
+    """The dW kernel's scaled inner loop is exact only for inputs >= -MAX, magnitudes that do not underflow
+    when scaled and gradients below 2^100; anything else must take its unscaled loop and still match."""
+    import torch
+    from snntc_2023_b200 import ops
+    seed, B, I, J, bv = 24, 33, 70, 64, 1.0
+    x, w = P.make_inputs(seed, (B, I), (I + 1, J), "test")
+    g = np.random.default_rng(4).standard_normal((B, J)).astype(np.float32)
+    if odd == "below_minus_max":
+        x[0, 0] = -3e5
+    elif odd == "tiny":
+        x[1, 1] = 1e-30
+    else:
+        g[2, 3] = 1e36
+    params = O.fc_params(biasvolt=bv)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    out = ops.snn_fc(xd, wd, params)
+    outc = out.cpu().numpy()
+    dx, dw, _ = ops.snn_fc_grad(torch.from_numpy(g).cuda(), xd, wd, params, out)
+    ref = O.fc_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    with np.errstate(over="ignore", invalid="ignore"):
+        P.check_close(dw.cpu().numpy(), ref["dw"], "dW %s" % odd, abs_sum=ref["dw_abs"])
+        P.check_close(dx.cpu().numpy(), ref["dx"], "dX %s" % odd, abs_sum=ref["dx_abs"])
+
+
 def test_dense_repeatable():
     """No atomics on the dense path: two runs give identical bits."""
     import torch
