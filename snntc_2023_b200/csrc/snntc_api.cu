@@ -179,7 +179,7 @@ unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std:
 
 void snntc_set_overlap(int on) { snntc::g_overlap.store(on ? 1 : 0, std::memory_order_relaxed); }
 
-void snntc_profile_forward_parts(int mask) { snntc::g_forward_parts.store(mask & 15, std::memory_order_relaxed); }
+void snntc_profile_forward_parts(int mask) { snntc::g_forward_parts.store(mask & 63, std::memory_order_relaxed); }
 
 void snntc_profile_backward_parts(int mask) { snntc::g_backward_parts.store(mask & 3, std::memory_order_relaxed); }
 

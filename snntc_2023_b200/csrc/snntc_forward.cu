@@ -70,7 +70,7 @@ __device__ __forceinline__ int or3(int a, int b, int c) {
 // rounded, division-free tests for the outputs concerned, so the decision is the reference's. An output
 // whose q is non-positive but which the reference test did not fire (possible only when q is within an
 // ulp of zero) keeps being tested exactly at every following step.
-template <int JPT, int CH, bool FULL>
+template <int JPT, int CH, bool FULL, bool VECW>
 __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
                                          float* __restrict__ y_row, float* __restrict__ inv_row) {
@@ -81,9 +81,11 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   int livemask[JPT];
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
-    const int j = jbase + lane + 32 * m;
+    // VECW: a lane owns JPT consecutive outputs and reads them with one 8- or 16-byte load (J % JPT == 0,
+    // so a lane is wholly inside or wholly outside the row); otherwise outputs lane + 32*m, 4-byte loads
+    const int j = VECW ? jbase + JPT * lane + m : jbase + lane + 32 * m;
     jok[m] = FULL || j < J;
-    jl[m] = jok[m] ? j : J - 1;
+    jl[m] = jok[m] ? j : (VECW ? J - JPT + m : J - 1);
     wsum[m] = -g.theta;
     ysum[m] = 0.f;
     if (g.has_bias) {  // the bias input (value biasvolt, weight row I) is always consumed first
@@ -99,7 +101,19 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   // first step needs no special case; with bias the previous input is the bias input itself.
   float xprev = g.has_bias ? g.biasvolt : 0.f;
 
-  const float* wl = w + (FULL ? jbase + lane : 0);
+  const float* wl = w + (VECW ? jl[0] : (FULL ? jbase + lane : 0));
+  auto load_weights = [&](const float* wrow, float (&wv)[JPT]) {
+    if (VECW && JPT == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(wrow));
+      wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
+    } else if (VECW && JPT == 2) {
+      const float2 v = __ldg(reinterpret_cast<const float2*>(wrow));
+      wv[0] = v.x; wv[1] = v.y;
+    } else {
+#pragma unroll
+      for (int m = 0; m < JPT; ++m) wv[m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
+    }
+  };
 
   // one step for all JPT outputs of this lane: sign test, (rarely) exact test, then consume
   auto step = [&](const float x, const float (&wv)[JPT]) {
@@ -141,9 +155,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     for (int u = 0; u < CH; ++u) {
       const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
       xs[u] = __uint_as_float(e.x);
-      const float* wrow = wl + e.y;
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) wv[u][m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
+      load_weights(wl + e.y, wv[u]);
     }
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
@@ -155,10 +167,8 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   if (!all_done) {
     for (; k < nvalid; ++k) {
       const WalkEntry e = __ldcg(ents + k);
-      const float* wrow = wl + e.y;
       float wv[JPT];
-#pragma unroll
-      for (int m = 0; m < JPT; ++m) wv[m] = FULL ? __ldg(wrow + 32 * m) : __ldg(wrow + jl[m]);
+      load_weights(wl + e.y, wv);
       step(__uint_as_float(e.x), wv);
     }
   }
@@ -179,7 +189,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       if (yv >= g.maxv) { yv = g.maxv; iv = 0.f; }
     }
     if (jok[m]) {
-      const int j = jbase + lane + 32 * m;
+      const int j = VECW ? jbase + JPT * lane + m : jbase + lane + 32 * m;
       y_row[j] = yv;
       inv_row[j] = iv;
     }
@@ -285,6 +295,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
     }
     xprev = x;
   };
+  const unsigned lane_off = (unsigned)jl[0];   // element offset of this lane's first pair within a weight row
   auto load_pair = [&](const float* wrow, int m) -> uint64_t {
     return __ldg(reinterpret_cast<const unsigned long long*>(FULL ? wrow + 64 * m : wrow + jl[m]));
   };
@@ -298,9 +309,16 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
     for (int u = 0; u < CH; ++u) {
       const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
       xs[u] = __uint_as_float(e.x);
-      const float* wrow = wl + e.y;
+      if (JP == 1) {
+        // one pair per lane: a 32-bit element offset from the (uniform) weight base measured faster than a
+        // 64-bit per-lane pointer plus the entry's offset
+        wv[u][0] = __ldg(reinterpret_cast<const unsigned long long*>(
+            reinterpret_cast<const char*>(w) + (size_t)((e.y + lane_off) * 4u)));
+      } else {
+        const float* wrow = wl + e.y;
 #pragma unroll
-      for (int m = 0; m < JP; ++m) wv[u][m] = load_pair(wrow, m);
+        for (int m = 0; m < JP; ++m) wv[u][m] = load_pair(wrow, m);
+      }
     }
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
@@ -463,20 +481,24 @@ __device__ __forceinline__ void bitonic_sort_cta(u64* keys, int n, int tid) {
 // warp instead of 16 bytes and 4 KB, which lets a third CTA (24 instead of 16 rows) be resident per SM
 // at fan-in 577 -- the kernel is bound by shared-memory latency, so resident rows are what it needs.
 struct SortBuffers {
-  uint32_t* key[2];
-  unsigned short* idx[2];
-  unsigned* hist;   // [0,256): digit 0 in bits 0..15, digit 1 in bits 16..31; [256,512): digits 2 and 3
+  uint32_t* key;         // buffer b at key + b*I
+  unsigned short* idx;   // buffer b at idx + b*I
+  unsigned* hist;        // [0,256): digit 0 in bits 0..15, digit 1 in bits 16..31; [256,512): digits 2 and 3
+  int I;
+  // (the two buffers are addressed by offset, not through an array of pointers: a pointer picked at run time
+  // out of an array loses its address space and every access through it becomes a generic load or store)
+  __device__ __forceinline__ uint32_t* keys(int b) const { return key + b * I; }
+  __device__ __forceinline__ unsigned short* idxs(int b) const { return idx + b * I; }
 };
 __host__ __device__ __forceinline__ size_t sort_bytes_per_warp(int I) {
   return (((size_t)12 * I + 15) & ~(size_t)15) + 2048;
 }
 __device__ __forceinline__ SortBuffers sort_buffers(unsigned char* base, int I) {
   SortBuffers b;
-  b.key[0] = reinterpret_cast<uint32_t*>(base);
-  b.key[1] = b.key[0] + I;
-  b.idx[0] = reinterpret_cast<unsigned short*>(b.key[1] + I);
-  b.idx[1] = b.idx[0] + I;
+  b.key = reinterpret_cast<uint32_t*>(base);
+  b.idx = reinterpret_cast<unsigned short*>(b.key + 2 * I);
   b.hist = reinterpret_cast<unsigned*>(base + (((size_t)12 * I + 15) & ~(size_t)15));
+  b.I = I;
   return b;
 }
 
@@ -523,8 +545,8 @@ __device__ __forceinline__ int gather_row_compact(const Geometry& g, const float
       if (keep) {
         const uint32_t key = float_to_sortable(v[q]);
         const int pos = n + __popc(mask & ((1u << lane) - 1u));
-        sb.key[0][pos] = key;
-        sb.idx[0][pos] = (unsigned short)i;
+        sb.key[pos] = key;
+        sb.idx[pos] = (unsigned short)i;
         if (counts) {
           atomicAdd(&sb.hist[key & 255u], 1u);
           atomicAdd(&sb.hist[(key >> 8) & 255u], 1u << 16);
@@ -540,13 +562,29 @@ __device__ __forceinline__ int gather_row_compact(const Geometry& g, const float
 
 // n <= 32: rank every (key, index) against the others with shuffles. buffers 0 -> 1, one warp.
 __device__ __forceinline__ void sort_small_compact(const SortBuffers& sb, int n, int lane) {
-  const u64 e = lane < n ? (((u64)sb.key[0][lane] << 32) | sb.idx[0][lane]) : ~0ull;
+  const u64 e = lane < n ? (((u64)sb.key[lane] << 32) | sb.idx[lane]) : ~0ull;
   int rank = 0;
   for (int j = 0; j < n; ++j) {
     const u64 o = __shfl_sync(0xffffffffu, e, j);
     rank += o < e;
   }
-  if (lane < n) { sb.key[1][rank] = (uint32_t)(e >> 32); sb.idx[1][rank] = (unsigned short)e; }
+  if (lane < n) { sb.keys(1)[rank] = (uint32_t)(e >> 32); sb.idxs(1)[rank] = (unsigned short)e; }
+}
+
+// Lanes of the warp whose 8-bit digit equals this lane's: eight ballots, one per bit (lanes without a key carry
+// a digit >= 256 that is unique to them and are masked out by `actmask`). The match instruction gives the
+// same mask in one go but runs on the SM's single address-divergence unit (about 55 cycles each), which bounds
+// the kernel when every batch uses it; the ballots cost some 40 ALU instructions on the issuing scheduler's own
+// pipe. The sort alternates between the two so that neither unit is the bottleneck.
+__device__ __forceinline__ unsigned digit_peers(unsigned d, unsigned actmask) {
+  unsigned same1 = actmask, any0 = 0u;   // AND of the ballots of this lane's set bits, OR of those of its clear bits
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const bool bit = (d >> b) & 1u;
+    const unsigned m = __ballot_sync(0xffffffffu, bit);
+    if (bit) same1 &= m; else any0 |= m;
+  }
+  return same1 & ~any0;
 }
 
 // Stable LSD radix sort, 8 bits per pass, one warp; returns which buffer (0/1) holds the result.
@@ -580,10 +618,10 @@ __device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int
       run += c[q];
     }
     __syncwarp();
-    const uint32_t* srcK = sb.key[cur];
-    const unsigned short* srcI = sb.idx[cur];
-    uint32_t* dstK = sb.key[cur ^ 1];
-    unsigned short* dstI = sb.idx[cur ^ 1];
+    const uint32_t* srcK = sb.keys(cur);
+    const unsigned short* srcI = sb.idxs(cur);
+    uint32_t* dstK = sb.keys(cur ^ 1);
+    unsigned short* dstI = sb.idxs(cur ^ 1);
     const int shift = 8 * p;
     constexpr int kSB = 4;   // batches of 32 keys whose loads and digit matches go ahead of the serial part
     for (int i0 = 0; i0 < n; i0 += 32 * kSB) {
@@ -600,7 +638,8 @@ __device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int
         d[q] = act[q] ? (k[q] >> shift) & 255u : 256u + (unsigned)lane;
       }
 #pragma unroll
-      for (int q = 0; q < kSB; ++q) peers[q] = __match_any_sync(0xffffffffu, d[q]);
+      for (int q = 0; q < kSB; ++q)
+        peers[q] = (q & 1) ? digit_peers(d[q], __ballot_sync(0xffffffffu, act[q])) : __match_any_sync(0xffffffffu, d[q]);
 #pragma unroll
       for (int q = 0; q < kSB; ++q) {
         if (i0 + 32 * q < n) {   // warp-uniform
@@ -649,8 +688,8 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
     else res = radix_sort_row_compact(sb, n, lane);
     __syncwarp();
     WalkEntry* dst = keys_g + (size_t)r * istride;
-    const uint32_t* rk = sb.key[res];
-    const unsigned short* ri = sb.idx[res];
+    const uint32_t* rk = sb.keys(res);
+    const unsigned short* ri = sb.idxs(res);
     for (int i = lane; i < n; i += 32)
       dst[i] = make_uint2(__float_as_uint(sortable_to_float(rk[i])), (uint32_t)ri[i] * (uint32_t)g.J);
     if (lane == 0) nvalid_g[r] = n;
@@ -687,7 +726,7 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* _
 }
 
 // Walk kernel: every warp takes (row, block of 32*JPT outputs) items, adjacent warps share a row.
-template <int JPT>
+template <int JPT, bool VECW>
 __global__ void __launch_bounds__(kFwdThreads)
 snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                 const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
@@ -705,9 +744,9 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __ldg(nvalid_g + r);
     if (full_j)
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), true>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
     else
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), false>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
   }
 }
 
@@ -740,7 +779,7 @@ int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of k
 
 size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
 
-template <int JPT>
+template <int JPT, bool VECW>
 int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
                 const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end) {
   const int jchunks = (g.J + 32 * JPT - 1) / (32 * JPT);
@@ -748,7 +787,7 @@ int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g,
   long grid = (items + kFwdWarps - 1) / kFwdWarps;
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
-  snn_walk_kernel<JPT><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  snn_walk_kernel<JPT, VECW><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -799,10 +838,16 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     }
     return best_c;
   };
-  // packed walk (two outputs per 64-bit register) whenever the output pairs are 8-byte aligned
-  const bool pairs = (g.J % 2 == 0) && (reinterpret_cast<uintptr_t>(w) % 8 == 0);
+  // Variants of the walk: 1 = output pairs in 64-bit registers (two-lane FP32 instructions), 2 = scalar with
+  // outputs lane + 32*m, 3 = scalar with consecutive outputs per lane read by one 8/16-byte load.
+  const bool al8 = (g.J % 2 == 0) && (reinterpret_cast<uintptr_t>(w) % 8 == 0);
+  const bool al16 = (g.J % 4 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0);
+  int variant = al8 ? (g.J <= 64 ? 1 : 3) : 2;
+  if (((fparts >> 4) & 3) != 0) variant = (fparts >> 4) & 3;   // measurement aid
+  if (variant == 1 && !al8) variant = 2;
+  if (variant == 3 && !al8) variant = 2;
   int jsel;
-  if (pairs) {
+  if (variant == 1) {
     const double cost[3] = {kWalk2Cost[0], kWalk2Cost[1], kWalk2Cost[2]};
     const int ctas[3] = {kWalk2Ctas[0], kWalk2Ctas[1], kWalk2Ctas[2]};
     jsel = pick(64, cost, ctas, g.J <= 64 ? 0 : (g.J <= kWalk2TopJ ? 1 : 2));
@@ -812,16 +857,21 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
   }
   if (((fparts >> 2) & 3) != 0) jsel = ((fparts >> 2) & 3) - 1;   // measurement aid: force the outputs per lane
+  if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (pairs) {
+    if (variant == 1) {
       if (jsel == 0) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
       if (jsel == 1) return launch_walk2<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
       return launch_walk2<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     }
-    if (jsel == 0) return launch_walk<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    if (jsel == 1) return launch_walk<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    return launch_walk<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (variant == 3) {
+      if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      return launch_walk<4, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    }
+    if (jsel == 1) return launch_walk<2, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    return launch_walk<4, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
   };
 
   const size_t budget = (size_t)li.max_smem_optin - 1024;

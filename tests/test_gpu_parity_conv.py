@@ -21,6 +21,7 @@ CONV_CASES = [
     (49, 4, 8, 8, 3, 3, 3, 1, 1, 64, 1.0, "SAME", "cfg"),
     (50, 1, 5, 5, 1, 1, 1, 1, 1, 1, 1.0, "SAME", "test"),
     (51, 2, 9, 9, 16, 7, 7, 2, 2, 40, 1.0, "SAME", "cfg"),
+    (52, 5, 64, 64, 3, 3, 3, 1, 1, 64, 1.0, "SAME", "cfg"),   # 20480 rows: many more than resident warps
 ]
 
 

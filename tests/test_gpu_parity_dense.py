@@ -21,6 +21,8 @@ DENSE_CASES = [
     (20, 6, 4097, 512, 1.0, "cfg"),
     (22, 40, 31, 64, 1.0, "test"),      # <= 32 inputs: shuffle rank sort
     (23, 40, 33, 128, 0.0, "test"),
+    (25, 18945, 24, 64, 1.0, "cfg"),    # many more rows than resident warps, odd row count
+    (26, 19000, 40, 36, 0.0, "test"),   # the same with a ragged last block of outputs
 ]
 
 
