@@ -502,15 +502,27 @@ __device__ __forceinline__ SortBuffers sort_buffers(unsigned char* base, int I) 
   return b;
 }
 
-// gather as gather_row, into (key[0], idx[0]); counts = false for rows that are ranked with shuffles
+// Where the taps of a conv row sit, relative to the row's top-left input pixel: built once per CTA, the same
+// for every row. off[i] = ((kh*W + kw)*C + c) in elements, khw[i] = kh << 8 | kw (Kh, Kw <= 255). Both arrays
+// are padded to a multiple of 128 entries so that a whole batch of loads may index them.
+struct TapTable {
+  const int* off;
+  const unsigned short* khw;
+};
+__host__ __device__ __forceinline__ int tap_entries(int I) { return (I + 127) & ~127; }
+__host__ __device__ __forceinline__ size_t tap_table_bytes(int I) { return (size_t)tap_entries(I) * 6; }
+
+// Loads one row, drops inputs above MAX-0.1 and writes (sortable key, source index) of the rest to buffer 0
+// in index order; returns their number and the smallest / largest key. One warp, no divergent branch: a tap
+// outside the image (or past the end of the row) is a predicated-off load that reads as MAX and is dropped.
 __device__ __forceinline__ int gather_row_compact(const Geometry& g, const float* __restrict__ x, int r, int lane,
-                                                  const SortBuffers& sb, bool counts, const TapCursor& start) {
+                                                  const SortBuffers& sb, const TapTable& tt,
+                                                  uint32_t& kmin, uint32_t& kmax) {
   const int I = g.I;
   const float maxcomp = g.maxv - 0.1f;
   int n = 0;
   int h0 = 0, w0 = 0;
   const float* xr = x + (size_t)r * I;
-  TapCursor cur = start;
   if (g.is_conv) {
     const int nw = r % g.Nw;
     const int t = r / g.Nw;
@@ -518,46 +530,75 @@ __device__ __forceinline__ int gather_row_compact(const Geometry& g, const float
     const int b = t / g.Nh;
     h0 = nh * g.Sh - g.pad_top;
     w0 = nw * g.Sw - g.pad_left;
-    xr = x + (size_t)b * g.H * g.W * g.C;
+    // the row's top-left input pixel; may lie outside the image, in which case it is never dereferenced
+    xr = x + ((ptrdiff_t)b * g.H * g.W + (ptrdiff_t)h0 * g.W + w0) * g.C;
   }
+  uint32_t lmin = 0xFFFFFFFFu, lmax = 0u;
+  const unsigned lt = (1u << lane) - 1u;
   constexpr int kBatch = 4;   // loads in flight per lane before anything depends on them
   for (int i0 = 0; i0 < I; i0 += 32 * kBatch) {
     float v[kBatch];
 #pragma unroll
     for (int q = 0; q < kBatch; ++q) {
       const int i = i0 + 32 * q + lane;
-      v[q] = g.maxv;
-      if (i < I) {
-        if (!g.is_conv) {
-          v[q] = __ldg(xr + i);
-        } else {
-          const int h = h0 + cur.kh, ww = w0 + cur.kw;
-          if (h >= 0 && h < g.H && ww >= 0 && ww < g.W) v[q] = __ldg(xr + ((size_t)h * g.W + ww) * g.C + cur.c);
-        }
+      bool ok = i < I;
+      ptrdiff_t o = i;
+      if (g.is_conv) {
+        const unsigned khw = tt.khw[i];
+        o = tt.off[i];
+        ok = ok && (unsigned)(h0 + (int)(khw >> 8)) < (unsigned)g.H && (unsigned)(w0 + (int)(khw & 255u)) < (unsigned)g.W;
       }
-      if (g.is_conv) cur.advance32(g);
+      v[q] = g.maxv;
+      if (ok) v[q] = __ldg(xr + o);
     }
 #pragma unroll
     for (int q = 0; q < kBatch; ++q) {
       const int i = i0 + 32 * q + lane;
-      const bool keep = (i < I) && !(v[q] > maxcomp);
+      const bool keep = !(v[q] > maxcomp);   // a predicated-off load holds MAX
       const unsigned mask = __ballot_sync(0xffffffffu, keep);
       if (keep) {
         const uint32_t key = float_to_sortable(v[q]);
-        const int pos = n + __popc(mask & ((1u << lane) - 1u));
+        const int pos = n + __popc(mask & lt);
         sb.key[pos] = key;
         sb.idx[pos] = (unsigned short)i;
-        if (counts) {
-          atomicAdd(&sb.hist[key & 255u], 1u);
-          atomicAdd(&sb.hist[(key >> 8) & 255u], 1u << 16);
-          atomicAdd(&sb.hist[256 + ((key >> 16) & 255u)], 1u);
-          atomicAdd(&sb.hist[256 + (key >> 24)], 1u << 16);
-        }
+        lmin = min(lmin, key);
+        lmax = max(lmax, key);
       }
       n += __popc(mask);
     }
   }
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) {
+    lmin = min(lmin, __shfl_xor_sync(0xffffffffu, lmin, d));
+    lmax = max(lmax, __shfl_xor_sync(0xffffffffu, lmax, d));
+  }
+  kmin = lmin;
+  kmax = lmax;
   return n;
+}
+
+// Rebase the keys of buffer 0 to key - kmin (order is kept, and the digits above the range of the row become
+// zero, so their passes are not needed at all) and count the lowest `passes` 8-bit digits. One warp.
+__device__ __forceinline__ void rebase_and_count(const SortBuffers& sb, int n, int lane, uint32_t kmin, int passes) {
+  for (int i0 = 0; i0 < n; i0 += 128) {
+    uint32_t k[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = i0 + 32 * q + lane;
+      k[q] = i < n ? sb.key[i] - kmin : 0u;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = i0 + 32 * q + lane;
+      if (i < n) {
+        sb.key[i] = k[q];
+        atomicAdd(&sb.hist[k[q] & 255u], 1u);
+        if (passes > 1) atomicAdd(&sb.hist[(k[q] >> 8) & 255u], 1u << 16);
+        if (passes > 2) atomicAdd(&sb.hist[256 + ((k[q] >> 16) & 255u)], 1u);
+        if (passes > 3) atomicAdd(&sb.hist[256 + (k[q] >> 24)], 1u << 16);
+      }
+    }
+  }
 }
 
 // n <= 32: rank every (key, index) against the others with shuffles. buffers 0 -> 1, one warp.
@@ -588,11 +629,11 @@ __device__ __forceinline__ unsigned digit_peers(unsigned d, unsigned actmask) {
 }
 
 // Stable LSD radix sort, 8 bits per pass, one warp; returns which buffer (0/1) holds the result.
-__device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int n, int lane) {
+__device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int n, int lane, int passes) {
   int cur = 0;
   const unsigned lt = (1u << lane) - 1u;
 #pragma unroll 1
-  for (int p = 0; p < 4; ++p) {
+  for (int p = 0; p < passes; ++p) {
     unsigned* h = sb.hist + ((p >> 1) << 8);
     const int fs = (p & 1) << 4;   // this digit's 16-bit field inside the packed word
     unsigned wds[8], c[8], s = 0;
@@ -672,26 +713,57 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int I = g.I;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpc = blockDim.x >> 5;
-  const SortBuffers sb = sort_buffers(smem_raw + (size_t)warp * sort_bytes_per_warp(I), I);
-  TapCursor start = {0, 0, 0};
-  if (g.is_conv) start.init(g, lane);
-  const bool tiny = I <= 32;   // ranked with shuffles: no digit histograms needed
-  for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
-    if (!tiny) {
-      for (int q = lane; q < 512; q += 32) sb.hist[q] = 0u;
-      __syncwarp();
+  // conv: the tap table of the CTA comes first, then the warps' buffers
+  TapTable tt = {nullptr, nullptr};
+  unsigned char* warp_base = smem_raw;
+  if (g.is_conv) {
+    int* off = reinterpret_cast<int*>(smem_raw);
+    unsigned short* khw = reinterpret_cast<unsigned short*>(off + tap_entries(I));
+    for (int i = threadIdx.x; i < tap_entries(I); i += blockDim.x) {
+      int o = 0;
+      unsigned kk = 0;
+      if (i < I) {
+        const int tap = i / g.C, c = i - tap * g.C;
+        const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
+        o = (kh * g.W + kw) * g.C + c;
+        kk = (unsigned)(kh << 8 | kw);
+      }
+      off[i] = o;
+      khw[i] = (unsigned short)kk;
     }
-    const int n = gather_row_compact(g, x, r, lane, sb, !tiny, start);
+    tt.off = off;
+    tt.khw = khw;
+    warp_base += (tap_table_bytes(I) + 15) & ~(size_t)15;
+    __syncthreads();
+  }
+  const SortBuffers sb = sort_buffers(warp_base + (size_t)warp * sort_bytes_per_warp(I), I);
+  for (int r = row_begin + blockIdx.x * wpc + warp; r < row_end; r += gridDim.x * wpc) {
+    uint32_t kmin, kmax;
+    const int n = gather_row_compact(g, x, r, lane, sb, tt, kmin, kmax);
     __syncwarp();
-    int res;
-    if (n <= 32) { sort_small_compact(sb, n, lane); res = 1; }
-    else res = radix_sort_row_compact(sb, n, lane);
+    int res = 0;
+    uint32_t base = 0u;   // added back to the keys on the way out
+    if (n > 32) {
+      const uint32_t range = kmax - kmin;
+      const int passes = (39 - __clz(range | 1u)) >> 3;   // 8-bit digits that cover the range (1 when range < 256)
+      if (range != 0u) {
+        for (int q = lane; q < 512; q += 32) sb.hist[q] = 0u;
+        __syncwarp();
+        rebase_and_count(sb, n, lane, kmin, passes);
+        __syncwarp();
+        res = radix_sort_row_compact(sb, n, lane, passes);
+        base = kmin;
+      }   // else: every key is the same, index order is the sorted order
+    } else {
+      sort_small_compact(sb, n, lane);
+      res = 1;
+    }
     __syncwarp();
     WalkEntry* dst = keys_g + (size_t)r * istride;
     const uint32_t* rk = sb.keys(res);
     const unsigned short* ri = sb.idxs(res);
     for (int i = lane; i < n; i += 32)
-      dst[i] = make_uint2(__float_as_uint(sortable_to_float(rk[i])), (uint32_t)ri[i] * (uint32_t)g.J);
+      dst[i] = make_uint2(__float_as_uint(sortable_to_float(rk[i] + base)), (uint32_t)ri[i] * (uint32_t)g.J);
     if (lane == 0) nvalid_g[r] = n;
     __syncwarp();
   }
@@ -876,7 +948,8 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
 
   const size_t budget = (size_t)li.max_smem_optin - 1024;
   const size_t per_warp = sort_bytes_per_warp(g.I);
-  if (per_warp > budget || g.I > 65535) {
+  const size_t table_min = g.is_conv ? ((tap_table_bytes(g.I) + 15) & ~(size_t)15) : 0;
+  if (table_min + per_warp > budget || g.I > 65535 || (g.is_conv && (g.Kh > 255 || g.Kw > 255))) {
     // rows too long for the warp sort: one CTA-wide bitonic sort per row, then the walk
     const size_t smem = (size_t)g.I * sizeof(u64);
     if (smem > budget) return E_UNSUPPORTED;
@@ -890,18 +963,19 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   }
 
   // warps per CTA and CTAs per SM: the combination that keeps the most rows (warps) resident per SM
+  const size_t table = g.is_conv ? ((tap_table_bytes(g.I) + 15) & ~(size_t)15) : 0;
   int wpc = 1, ctas_per_sm = 1;
   {
     int best = 0;
     for (int cand = kFwdWarps; cand >= 1; --cand) {
-      if (per_warp * cand > budget) continue;
-      int c = (int)(((size_t)li.max_smem_optin) / (per_warp * cand + 1024));
+      if (table + per_warp * cand > budget) continue;
+      int c = (int)(((size_t)li.max_smem_optin) / (table + per_warp * cand + 1024));
       if (c > 4) c = 4;
       if (c < 1) c = 1;
       if (cand * c > best) { best = cand * c; wpc = cand; ctas_per_sm = c; }
     }
   }
-  const size_t smem = per_warp * wpc;
+  const size_t smem = table + per_warp * wpc;
   if (cudaFuncSetAttribute(snn_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
     return E_CUDA;
   auto sort = [&](cudaStream_t st, int r0, int r1) -> int {
