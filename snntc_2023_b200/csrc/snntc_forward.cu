@@ -124,9 +124,11 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     if (JPT == 2) orall |= q[1];
     if (JPT == 4) orall = or3(or3(q[0], q[1], q[2]), q[3], 0);
     if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
-      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive
+      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive (usually one
+      // of the lane's outputs in one lane: skip the others with a warp-uniform test each)
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
+        if (JPT > 1 && !__any_sync(0xffffffffu, q[m] < 0)) continue;
         const bool fire = (q[m] < 0) & (livemask[m] != 0) & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
         if (fire) {
           livemask[m] = 0;  // spike lies in (previous input, x]: keep the sums aside ...
