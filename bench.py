@@ -234,9 +234,10 @@ class NetWorkload:
         specs, shape, classes = net_spec(config)
         weights = nets.spec_weights(specs, 1000 * (list(CONFIGS).index(config) + 1))
         self.net = nets.SnnNet(specs, weights=weights, device=device)
-        self.flat = torch.nn.Parameter(self.net.flat_param)
-        self.flat.grad = self.net.flat_grad
-        self.opt = torch.optim.Adam([self.flat], lr=1e-5, fused=True, capturable=True)
+        from snntc_2023_b200 import train
+        self.train = train
+        # Keras-formulation Adam over the flat parameter / gradient buffers (snntc-mnist.py:70), one kernel
+        self.opt = train.Adam(self.net.flat_param, self.net.flat_grad, lr=1e-5)
         self.graphed = None
         self.h2d_bytes = batch * int(np.prod(shape)) * 4 + batch * 8
         self.d2h_bytes = 4
@@ -264,7 +265,7 @@ class NetWorkload:
     def _eager_step(self, dev_batch):
         torch = self.torch
         t, lab = dev_batch
-        z = torch.exp(t)
+        z = self.train.encode(t, one_minus=False)
         loss = self.net.loss(z, lab)
         loss.backward()
         if self.world > 1 and self.collective:

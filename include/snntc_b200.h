@@ -116,6 +116,51 @@ SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx,
                                      void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Inference-only forward: SnnFc / SnnCv writing only the spike values, out[B,J] / out[B,Nh,Nw,Kc], without
+ * the 1/(sum w - theta) half that only the gradient operators read. Same arguments, workspace
+ * (snntc_fc_forward_workspace_bytes / snntc_cv_forward_workspace_bytes) and values as snntc_fc_forward /
+ * snntc_cv_forward. The reference has one operator for training and evaluation (snntc-mnist.py:88-94 calls
+ * the training forward with training=False); this is its serving-side half.
+ */
+SNNTC_API int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ,
+                             int B, int I, int w_rows, int J,
+                             void* workspace, size_t workspace_bytes, void* stream);
+SNNTC_API int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                             int B, int H, int W, int C, int w_rows, int Kc,
+                             int pad_top, int pad_left, int Nh, int Nw,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * The rest of a training step of the reference's example trainers, which the reference runs as TensorFlow
+ * graph ops: each is one or two kernels over flat fp32 device buffers, queued on `stream`.
+ *
+ * snntc_encode       x[e] = exp(scale * (one_minus ? 1 - p[e] : p[e]))   (snntc-mnist.py:75: exp(1.0*(1-images)))
+ * snntc_loss_ce      SNN_TC_Modules.loss_func (SNN_TC_Modules.py:286-288): softmax cross-entropy on the negated
+ *                    spike times y[B,J] against integer labels[B] (int64). sums2[0] += loss_scale * sum_b loss_b,
+ *                    sums2[1] += number of samples whose arg-min_j y equals the label (snntc-mnist.py:82); the
+ *                    caller zeroes sums2. grad (may be null) receives d(sum_b loss_b)/dy * grad_scale, i.e.
+ *                    -(softmax(-y) - onehot) * grad_scale; use loss_scale = grad_scale = 1/B for the mean.
+ * snntc_weight_cost  MyModel.constraint_cost for one weight tensor w[rows,J] (snntc-mnist.py:55-59):
+ *                    cost[0] += K * mean_j max(0, 1 - sum_i w_ij) + K2 * mean(w^2); gw (may be null) +=
+ *                    its gradient. workspace: snntc_weight_cost_workspace_bytes(J) bytes.
+ * snntc_adam_step    tf.keras.optimizers.Adam (snntc-mnist.py:70) on n elements: g is multiplied by grad_scale
+ *                    first (1/world size for an all-reduced sum). step[0] is a device int holding the number of
+ *                    steps taken so far (0 before the first); the call reads it for the bias correction and
+ *                    increments it, so a captured CUDA graph can be replayed. eps is added to sqrt(v) (Keras: 1e-7).
+ * snntc_sgdm_step    tf.keras.optimizers.SGD(momentum) (snntc-imagenet.py:238): vel = momentum*vel - lr*g; w += vel.
+ */
+SNNTC_API int snntc_encode(const float* p, float* x, size_t n, float scale, int one_minus, void* stream);
+SNNTC_API int snntc_loss_ce(const float* y, const long long* labels, float* grad, float* sums2, int B, int J,
+                            float loss_scale, float grad_scale, void* stream);
+SNNTC_API size_t snntc_weight_cost_workspace_bytes(int J);
+SNNTC_API int snntc_weight_cost(const float* w, float* gw, float* cost, int rows, int J, float K, float K2,
+                                void* workspace, size_t workspace_bytes, void* stream);
+SNNTC_API int snntc_adam_step(float* w, const float* g, float* m, float* v, size_t n, float lr, float beta1,
+                              float beta2, float eps, float grad_scale, int* step, void* stream);
+SNNTC_API int snntc_sgdm_step(float* w, const float* g, float* vel, size_t n, float lr, float momentum,
+                              float grad_scale, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * SnnFcGrad without a caller workspace. This entry point has no counterpart in the reference.
  *
  * For callers that have no way to allocate device memory when the dense backward runs (an operator

@@ -197,6 +197,9 @@ class SNN_LRN(torch.nn.Module):
 def loss_func(logit=None, label=None):
     """Softmax cross-entropy on the NEGATED spike values, batch mean (reference :286-288). `label` is
     one-hot [B,classes] as in the reference, or an integer class vector [B]."""
+    if logit.is_cuda and logit.dtype == torch.float32 and logit.dim() == 2:
+        from . import train   # one kernel for loss and gradient instead of five framework launches
+        return train.loss_func(logit, label)
     logp = F.log_softmax(-logit, dim=1)
     if label.dim() == 1 and not label.is_floating_point():
         return F.nll_loss(logp, label)

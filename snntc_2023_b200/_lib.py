@@ -33,6 +33,14 @@ SYMBOLS = {
     "snntc_minpool_backward": (_INT, [_F, _F, _F] + [_SZ, _SZ, _F]),
     "snntc_fc_backward_noalloc": (_INT, [_F] * 8 + [_INT] * 4 + [_F]),
     "snntc_noalloc_scratch_bytes": (_SZ, []),
+    "snntc_fc_infer": (_INT, [_F, _F, _F, _F] + [_INT] * 4 + [_F, _SZ, _F]),
+    "snntc_cv_infer": (_INT, [_F] * 4 + [_INT] * 10 + [_F, _SZ, _F]),
+    "snntc_encode": (_INT, [_F, _F, _SZ, ctypes.c_float, _INT, _F]),
+    "snntc_loss_ce": (_INT, [_F, _F, _F, _F, _INT, _INT, ctypes.c_float, ctypes.c_float, _F]),
+    "snntc_weight_cost_workspace_bytes": (_SZ, [_INT]),
+    "snntc_weight_cost": (_INT, [_F, _F, _F, _INT, _INT, ctypes.c_float, ctypes.c_float, _F, _SZ, _F]),
+    "snntc_adam_step": (_INT, [_F, _F, _F, _F, _SZ] + [ctypes.c_float] * 5 + [_F, _F]),
+    "snntc_sgdm_step": (_INT, [_F, _F, _F, _SZ] + [ctypes.c_float] * 3 + [_F]),
 }
 OPTIONAL = {"snntc_minpool_forward", "snntc_minpool_backward", "snntc_fc_backward_noalloc",
             "snntc_noalloc_scratch_bytes"}

@@ -13,7 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsnntc_b200.so")
-SOURCES = ["snntc_forward.cu", "snntc_backward.cu", "snntc_pool.cu", "snntc_noalloc.cu", "snntc_api.cu"]
+SOURCES = ["snntc_forward.cu", "snntc_backward.cu", "snntc_pool.cu", "snntc_noalloc.cu", "snntc_train.cu",
+           "snntc_api.cu"]
 HEADERS = [os.path.join(CSRC, "snntc_common.cuh"), os.path.join(HERE, "..", "include", "snntc_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]

@@ -224,6 +224,16 @@ int snntc_fc_forward(const float* x, const float* w, const float* params6_host, 
   return run_forward(g, x, w, out_2BJ, workspace, workspace_bytes, stream);
 }
 
+int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ,
+                   int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w || !out_BJ) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
+  if (rc) return rc;
+  g.infer = 1;
+  return run_forward(g, x, w, out_BJ, workspace, workspace_bytes, stream);
+}
+
 size_t snntc_fc_backward_workspace_bytes(int B, int I, int w_rows, int J) {
   if (B <= 0 || I <= 0 || J <= 0 || w_rows < I) return 0;
   snntc::Geometry g; memset(&g, 0, sizeof(g));
@@ -255,6 +265,17 @@ int snntc_cv_forward(const float* x_nhwc, const float* w, const float* params12_
   snntc::Geometry g;
   int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
   if (rc) return rc;
+  return run_forward(g, x_nhwc, w, out, workspace, workspace_bytes, stream);
+}
+
+int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                   int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x_nhwc || !w || !out) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
+  if (rc) return rc;
+  g.infer = 1;
   return run_forward(g, x_nhwc, w, out, workspace, workspace_bytes, stream);
 }
 

@@ -18,6 +18,8 @@ struct Geometry {
   float maxv, theta, biasvolt;
   // conv only
   int B, H, W, C, Kh, Kw, Sh, Sw, pad_top, pad_left, Nh, Nw;
+  // forward only: 1 = inference (the output is [R,J] spike values; 1/(sum w - theta) is not written)
+  int infer;
 };
 
 struct LaunchInfo {

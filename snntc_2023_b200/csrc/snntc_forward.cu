@@ -193,7 +193,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     if (jok[m]) {
       const int j = VECW ? jbase + JPT * lane + m : jbase + lane + 32 * m;
       y_row[j] = yv;
-      inv_row[j] = iv;
+      if (inv_row != nullptr) inv_row[j] = iv;
     }
   }
 }
@@ -363,7 +363,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       if (jok[m]) {
         const int j = jbase + 2 * lane + 64 * m + h;
         y_row[j] = yv;
-        inv_row[j] = iv;
+        if (inv_row != nullptr) inv_row[j] = iv;
       }
     }
   }
@@ -809,7 +809,7 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
   const int jchunks = (J + 32 * JPT - 1) / (32 * JPT);
   const bool full_j = (J % (32 * JPT)) == 0;
   float* __restrict__ y_out = out;
-  float* __restrict__ inv_out = out + (size_t)R * J;
+  float* __restrict__ inv_out = g.infer ? nullptr : out + (size_t)R * J;
   const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
   for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
@@ -818,9 +818,9 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __ldg(nvalid_g + r);
     if (full_j)
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
     else
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row<JPT, (JPT >= 4 ? 4 : 8), false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
   }
 }
 
@@ -834,7 +834,7 @@ snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const i
   const int jchunks = (J + 64 * JP - 1) / (64 * JP);
   const bool full_j = (J % (64 * JP)) == 0;
   float* __restrict__ y_out = out;
-  float* __restrict__ inv_out = out + (size_t)R * J;
+  float* __restrict__ inv_out = g.infer ? nullptr : out + (size_t)R * J;
   const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
   for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
@@ -843,9 +843,9 @@ snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const i
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __ldg(nvalid_g + r);
     if (full_j)
-      walk_row2<JP, (JP >= 2 ? 4 : 8), true>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row2<JP, (JP >= 2 ? 4 : 8), true>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
     else
-      walk_row2<JP, (JP >= 2 ? 4 : 8), false>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, inv_out + (size_t)r * J);
+      walk_row2<JP, (JP >= 2 ? 4 : 8), false>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
   }
 }
 

@@ -127,6 +127,23 @@ def snn_fc(inp, weight, params):
     return out
 
 
+def snn_fc_infer(inp, weight, params):
+    """Spike values only, [B,J]: SnnFc without the 1/(sum w - theta) half (snntc_fc_infer)."""
+    lib = _lib.load()
+    x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 6)
+    if x.dim() != 2 or w.dim() != 2:
+        raise ValueError("snn_fc_infer expects in[B,I] and weight[rows,J]")
+    B, I = x.shape
+    rows, J = w.shape
+    with torch.cuda.device(x.device):
+        out = torch.empty((B, J), dtype=torch.float32, device=x.device)
+        ws, wsb = _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
+        rc = lib.snntc_fc_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
+                                _ptr(ws), wsb, _stream(x))
+    _lib.check(rc, "SnnFc (inference)")
+    return out
+
+
 def snn_fc_grad(grad, inp, weight, params, oldout, need_input_grad=True, grad_weight_out=None):
     """grad may be the packed [2B,J] tensor or just its first B rows (only those are read)."""
     lib = _lib.load()
@@ -187,6 +204,22 @@ def snn_cv(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
                                   pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
         Profile.end(ev, x, "cv_forward", (B * Nh * Nw, rows, Kc))
     _lib.check(rc, "SnnCv")
+    return out
+
+
+def snn_cv_infer(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
+    """Spike values only, [B,Nh,Nw,Kc]: SnnCv without the 1/(sum w - theta) half (snntc_cv_infer)."""
+    lib = _lib.load()
+    x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 12)
+    B, H, W, C, rows, Kc, Kh, Kw, pt, pl, Nh, Nw = _cv_dims(x, w, p, pad_top, pad_left, Nh, Nw)
+    if Nh <= 0 or Nw <= 0:
+        raise ValueError("snn_cv_infer: kernel larger than the (padded) input")
+    with torch.cuda.device(x.device):
+        out = torch.empty((B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
+        ws, wsb = _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
+        rc = lib.snntc_cv_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
+                                pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
+    _lib.check(rc, "SnnCv (inference)")
     return out
 
 
@@ -304,11 +337,20 @@ class _SnnCvLayer(torch.autograd.Function):
         return dx, (None if ctx.sink is not None else dw), None, None, None
 
 
+def _no_grad_needed(X, W):
+    return not (torch.is_grad_enabled() and (X.requires_grad or W.requires_grad))
+
+
 def snn_fc_layer(X, W, params, grad_sink=None):
+    if _no_grad_needed(X, W) and Profile.records is None:   # evaluation: nothing will read 1/(sum w - theta)
+        return snn_fc_infer(X, W, params)
     return _SnnFcLayer.apply(X, W, params, grad_sink)
 
 
 def snn_cv_layer(X, W, params, geom, grad_sink=None):
+    if _no_grad_needed(X, W) and Profile.records is None:
+        pt, pl, Nh, Nw = geom
+        return snn_cv_infer(X, W, params, pt, pl, Nh, Nw)
     return _SnnCvLayer.apply(X, W, params, geom, grad_sink)
 
 
