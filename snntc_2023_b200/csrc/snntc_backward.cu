@@ -460,49 +460,52 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
   const int ly_r = VEC ? (tid >> 4) : (tid >> 6);
   const int li = i0 + lx_c;   // fan-in index this thread loads
   const int lj = j0 + ly_c;   // output index this thread loads
-  int l_kh = 0, l_kw = 0, l_c = 0;
+  // conv: this loader's column is one tap (kh, kw, c) of the receptive field, the same for every row; where a
+  // row's receptive field starts (element offset of its top-left input pixel, which may lie outside the image,
+  // and that pixel's h, w) is worked out once per row by 16 threads, two tiles ahead, into rowinfo
+  int l_kh = 0, l_kw = 0, l_off = 0;
   if (g.is_conv && li < I) {
     const int tap = li / g.C;
-    l_c = li - tap * g.C;
+    const int c = li - tap * g.C;
     l_kh = tap / g.Kw;
     l_kw = tap - l_kh * g.Kw;
+    l_off = (l_kh * g.W + l_kw) * g.C + c;
   }
-  // position of this loader's first x row (r_begin + lx_r) in the output grid, advanced incrementally
-  int c_b = 0, c_nh = 0, c_nw = 0;
-  if (g.is_conv) {
-    const int r = r_begin + lx_r;
-    c_nw = r % g.Nw;
-    const int t = r / g.Nw;
-    c_nh = t % g.Nh;
-    c_b = t / g.Nh;
-  }
-  auto advance = [&](int by) {  // move (c_b, c_nh, c_nw) forward by `by` rows
-    c_nw += by;
-    while (c_nw >= g.Nw) { c_nw -= g.Nw; if (++c_nh == g.Nh) { c_nh = 0; ++c_b; } }
+  __shared__ int4 rowinfo[2][kRT];   // .x element offset of the top-left pixel, .y its h, .z its w
+  auto fill_rowinfo = [&](int buf, int rb) {
+    if (g.is_conv && tid < kRT) {
+      const int r = rb + tid;
+      int4 ri = make_int4(0, -(1 << 24), -(1 << 24), 0);   // rows past the slice: every tap reads as outside
+      if (r < r_end) {
+        const int nw = r % g.Nw;
+        const int t = r / g.Nw;
+        const int nh = t % g.Nh;
+        const int b = t / g.Nh;
+        ri.y = nh * g.Sh - g.pad_top;
+        ri.z = nw * g.Sw - g.pad_left;
+        ri.x = ((b * g.H + ri.y) * g.W + ri.z) * g.C;
+      }
+      rowinfo[buf][tid] = ri;
+    }
   };
 
   float px[kRT / 2], py[kRT / 4], pu[kRT / 4];  // parked untouched until after the arithmetic, see dX
-  auto fetch = [&](int rb) {
+  auto fetch = [&](int rb, int ibuf) {
 #pragma unroll
     for (int q = 0; q < kRT / 2; ++q) {
-      const int r = rb + lx_r + 2 * q;
-      // padding of the tile: x=+inf, y=0, u=0 gives relu(y-x) = 0 and a zero product (never inf-inf)
-      float xv = CUDART_INF_F;
-      if (r < r_end) {
-        if (li < I) {
-          if (!g.is_conv) {
-            xv = __ldg(x + (size_t)r * I + li);
-          } else {
-            const int h = c_nh * g.Sh - g.pad_top + l_kh, ww = c_nw * g.Sw - g.pad_left + l_kw;
-            if (h >= 0 && h < g.H && ww >= 0 && ww < g.W)
-              xv = __ldg(x + (((size_t)c_b * g.H + h) * g.W + ww) * g.C + l_c);
-          }
-        } else if (li == I && g.has_bias) {
-          xv = g.biasvolt;
-        }
+      const int rl = lx_r + 2 * q;
+      const int r = rb + rl;
+      // padding of the tile: x=+inf, y=0, u=0 gives relu(y-x) = 0 and a zero product (never inf-inf).
+      // The loaded value must not be touched here (not even by a select): it is still in flight.
+      float xv = (li == I && g.has_bias && r < r_end) ? g.biasvolt : CUDART_INF_F;
+      if (!g.is_conv) {
+        if (r < r_end && li < I) xv = __ldg(x + (size_t)r * I + li);
+      } else {
+        const int4 ri = rowinfo[ibuf][rl];
+        const bool ok = li < I && (unsigned)(ri.y + l_kh) < (unsigned)g.H && (unsigned)(ri.z + l_kw) < (unsigned)g.W;
+        if (ok) xv = __ldg(x + (ptrdiff_t)ri.x + l_off);
       }
       px[q] = xv;
-      if (g.is_conv) advance(2);
     }
     if (VEC) {
       const int r = rb + ly_r;
@@ -586,8 +589,11 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     }
   };
 
+  fill_rowinfo(0, r_begin);
+  fill_rowinfo(1, r_begin + kRT);
+  __syncthreads();
   if (r_begin < r_end) {
-    fetch(r_begin);
+    fetch(r_begin, 0);
     park(0);
   }
   __syncthreads();
@@ -596,10 +602,11 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
   for (int rb = r_begin; rb < r_end; rb += kRT, ++it) {
     const int buf = it & 1;
     const bool more = rb + kRT < r_end;
-    if (more) fetch(rb + kRT);
+    if (more) fetch(rb + kRT, buf ^ 1);
     if (fast) reduce_tile(buf, std::true_type{});
     else reduce_tile(buf, std::false_type{});
     if (more) park(buf ^ 1);
+    fill_rowinfo(buf, rb + 2 * kRT);   // this tile's entry was last read one iteration ago
     __syncthreads();
   }
 
