@@ -429,7 +429,7 @@ __device__ __forceinline__ float add_sat(float a, float b) {
 }
 
 template <bool VEC>   // VEC: J % 4 == 0, the y/u tiles are fetched with 16-byte loads
-__global__ void __launch_bounds__(kBwdThreads)
+__global__ void __launch_bounds__(kBwdThreads, 3)
 snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
               float scale, const int* __restrict__ exact_flag) {
