@@ -751,13 +751,9 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
       if (range != 0u) {
         for (int q = lane; q < 512; q += 32) sb.hist[q] = 0u;
         __syncwarp();
-#if !defined(SNNTC_SORT_EXPERIMENT) || SNNTC_SORT_EXPERIMENT >= 2
         rebase_and_count(sb, n, lane, kmin, passes);
         __syncwarp();
-#endif
-#if !defined(SNNTC_SORT_EXPERIMENT) || SNNTC_SORT_EXPERIMENT >= 3
         res = radix_sort_row_compact(sb, n, lane, passes);
-#endif
         base = kmin;
       }   // else: every key is the same, index order is the sorted order
     } else {
