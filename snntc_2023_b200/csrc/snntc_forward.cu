@@ -24,11 +24,6 @@ namespace {
 
 constexpr int kFwdThreads = 256;
 constexpr int kFwdWarps = kFwdThreads / 32;
-// packed walk: instructions per warp-step and resident CTAs per SM for 1 / 2 / 4 output pairs per lane, and the
-// widest fan-out that still uses 2 pairs per lane
-constexpr double kWalk2Cost[3] = {12.0, 17.0, 27.0};
-constexpr int kWalk2Ctas[3] = {4, 3, 2};
-constexpr int kWalk2TopJ = 1 << 30;
 
 typedef unsigned long long u64;
 
@@ -912,33 +907,25 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     }
     return best_c;
   };
-  // Variants of the walk: 1 = output pairs in 64-bit registers (two-lane FP32 instructions), 2 = scalar with
-  // outputs lane + 32*m, 3 = scalar with consecutive outputs per lane read by one 8/16-byte load.
+  // Variants of the walk: 1 = output pairs in 64-bit registers, 64 outputs per warp (fan-out <= 64, or few rows:
+  // more warps); 3 = scalar, 2 or 4 consecutive outputs per lane read by one 8/16-byte load (fan-out > 64);
+  // 2 = scalar with outputs lane + 32*m (odd fan-out or unaligned weights).
   const bool al8 = (g.J % 2 == 0) && (reinterpret_cast<uintptr_t>(w) % 8 == 0);
   const bool al16 = (g.J % 4 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  int variant = al8 ? (g.J <= 64 ? 1 : 3) : 2;
-  if (((fparts >> 4) & 3) != 0) variant = (fparts >> 4) & 3;   // measurement aid
-  if (variant == 1 && !al8) variant = 2;
-  if (variant == 3 && !al8) variant = 2;
-  int jsel;
-  if (variant == 1) {
-    const double cost[3] = {kWalk2Cost[0], kWalk2Cost[1], kWalk2Cost[2]};
-    const int ctas[3] = {kWalk2Ctas[0], kWalk2Ctas[1], kWalk2Ctas[2]};
-    jsel = pick(64, cost, ctas, g.J <= 64 ? 0 : (g.J <= kWalk2TopJ ? 1 : 2));
-  } else {
-    const double cost[3] = {19.0, 24.0, 39.0};
-    const int ctas[3] = {6, 4, 3};
-    jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
+  const double cost[3] = {19.0, 24.0, 39.0};
+  const int ctas[3] = {6, 4, 4};
+  int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
+  int variant = 2;
+  if (al8) variant = (g.J <= 64 || jsel < 2) ? 1 : 3;
+  if (((fparts >> 4) & 3) != 0) {   // measurement aid
+    variant = (fparts >> 4) & 3;
+    if (variant != 2 && !al8) variant = 2;
   }
   if (((fparts >> 2) & 3) != 0) jsel = ((fparts >> 2) & 3) - 1;   // measurement aid: force the outputs per lane
   if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (variant == 1) {
-      if (jsel == 0) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-      if (jsel == 1) return launch_walk2<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-      return launch_walk2<4>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    }
+    if (variant == 1) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     if (variant == 3) {
       if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
