@@ -97,12 +97,17 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   float xprev = g.has_bias ? g.biasvolt : 0.f;
 
   const float* wl = w + (VECW ? jl[0] : (FULL ? jbase + lane : 0));
-  auto load_weights = [&](const float* wrow, float (&wv)[JPT]) {
+  // VECW: one load per step, addressed by a 32-bit element offset from the (uniform) weight base -- measured
+  // faster than a 64-bit per-lane pointer plus the entry's offset
+  const unsigned lane_off = (unsigned)jl[0];
+  const char* wbase = reinterpret_cast<const char*>(w);
+  auto load_weights = [&](unsigned eoff, float (&wv)[JPT]) {
+    const float* wrow = wl + eoff;
     if (VECW && JPT == 4) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(wrow));
+      const float4 v = __ldg(reinterpret_cast<const float4*>(wbase + (size_t)((eoff + lane_off) * 4u)));
       wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
     } else if (VECW && JPT == 2) {
-      const float2 v = __ldg(reinterpret_cast<const float2*>(wrow));
+      const float2 v = __ldg(reinterpret_cast<const float2*>(wbase + (size_t)((eoff + lane_off) * 4u)));
       wv[0] = v.x; wv[1] = v.y;
     } else {
 #pragma unroll
@@ -152,7 +157,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     for (int u = 0; u < CH; ++u) {
       const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
       xs[u] = __uint_as_float(e.x);
-      load_weights(wl + e.y, wv[u]);
+      load_weights(e.y, wv[u]);
     }
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
@@ -165,7 +170,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     for (; k < nvalid; ++k) {
       const WalkEntry e = __ldcg(ents + k);
       float wv[JPT];
-      load_weights(wl + e.y, wv);
+      load_weights(e.y, wv);
       step(__uint_as_float(e.x), wv);
     }
   }
