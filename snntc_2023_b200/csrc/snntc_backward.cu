@@ -708,7 +708,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    if (vec && P >= 64 * kWideP) {
+    if (vec && P >= 64 * kWideP && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {   // it stores dx 16 bytes at a time
       dim3 gridw((unsigned)((P + kWideP - 1) / kWideP), (CH + kTile - 1) / kTile);
       snn_dx_wide_kernel<<<gridw, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
     } else if (vec) {

@@ -150,3 +150,48 @@ def test_dense_repeatable():
     a = ops.snn_fc_grad(g, xd, wd, params, out)
     b = ops.snn_fc_grad(g, xd, wd, params, out)
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+
+
+def test_walk_variants_agree_bit_for_bit():
+    """The library picks among several walk kernels (output pairs, consecutive outputs per lane, strided outputs,
+    1/2/4 outputs per lane); forced one by one through the measurement hook they must give identical bits."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    lib = _lib.load()
+    x, w = P.make_inputs(71, (50, 300), (301, 256), "cfg")
+    params = O.fc_params(biasvolt=1.0)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    ref = ops.snn_fc(xd, wd, params)
+    try:
+        for variant in (1, 2, 3):
+            for jsel in (0, 1, 2, 3):
+                lib.snntc_profile_forward_parts(3 | (jsel << 2) | (variant << 4))
+                out = ops.snn_fc(xd, wd, params)
+                assert torch.equal(out, ref), "variant %d, outputs-per-lane choice %d" % (variant, jsel)
+    finally:
+        lib.snntc_profile_forward_parts(3)
+
+
+def test_dense_unaligned_weight_and_input_pointers():
+    """Weights and inputs that start 4 bytes off a 16-byte boundary take the kernels without vector loads."""
+    import torch
+    from snntc_2023_b200 import ops
+    B, I, J = 40, 96, 64
+    x, w = P.make_inputs(72, (B, I), (I + 1, J), "test")
+    params = O.fc_params(biasvolt=1.0)
+    wflat = torch.empty((I + 1) * J + 1, device="cuda")
+    wd = wflat[1:].view(I + 1, J)
+    wd.copy_(torch.from_numpy(w))
+    xflat = torch.empty(B * I + 1, device="cuda")
+    xd = xflat[1:].view(B, I)
+    xd.copy_(torch.from_numpy(x))
+    assert wd.data_ptr() % 16 == 4 and xd.data_ptr() % 16 == 4
+    out = ops.snn_fc(xd, wd, params)
+    aligned = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params)
+    assert torch.equal(out, aligned)
+    g = np.random.default_rng(7).standard_normal((B, J)).astype(np.float32)
+    dx, dw, _ = ops.snn_fc_grad(torch.from_numpy(g).cuda(), xd, wd, params, out)
+    outc = out.cpu().numpy()
+    ref = O.fc_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    P.check_close(dx.cpu().numpy(), ref["dx"], "unaligned dX", abs_sum=ref["dx_abs"])
+    P.check_close(dw.cpu().numpy(), ref["dw"], "unaligned dW", abs_sum=ref["dw_abs"])
