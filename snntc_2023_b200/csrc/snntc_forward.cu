@@ -631,13 +631,48 @@ __device__ __forceinline__ unsigned digit_peers(unsigned d, unsigned actmask) {
 }
 
 // Stable LSD radix sort, 8 bits per pass, one warp; returns which buffer (0/1) holds the result.
-__device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int n, int lane, int passes) {
+// `top_bits` = significant bits of the last digit (the keys are rebased, so the last digit of a row whose values
+// span a few binades holds one or two bits): with at most two, that pass is a stable four-way split by two
+// ballots per batch, with the class bases read from the digit's histogram -- no ranking, no histogram updates.
+__device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int n, int lane, int passes, int top_bits) {
   int cur = 0;
   const unsigned lt = (1u << lane) - 1u;
 #pragma unroll 1
   for (int p = 0; p < passes; ++p) {
     unsigned* h = sb.hist + ((p >> 1) << 8);
     const int fs = (p & 1) << 4;   // this digit's 16-bit field inside the packed word
+    if (p == passes - 1 && top_bits <= 2) {
+      const unsigned c0 = (h[0] >> fs) & 0xFFFFu, c1 = (h[1] >> fs) & 0xFFFFu, c2 = (h[2] >> fs) & 0xFFFFu;
+      if (c0 == (unsigned)n) continue;   // (cannot happen for a rebased top digit with range > 0; kept for safety)
+      unsigned pos0 = 0u, pos1 = c0, pos2 = c0 + c1, pos3 = c0 + c1 + c2;   // next free slot of each class
+      const uint32_t* srcK = sb.keys(cur);
+      const unsigned short* srcI = sb.idxs(cur);
+      uint32_t* dstK = sb.keys(cur ^ 1);
+      unsigned short* dstI = sb.idxs(cur ^ 1);
+      const int shift = 8 * p;
+      for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        const bool act = i < n;
+        const uint32_t k = act ? srcK[i] : 0u;
+        const unsigned short ix = act ? srcI[i] : (unsigned short)0;
+        const unsigned cls = (k >> shift) & 3u;
+        const unsigned am = __ballot_sync(0xffffffffu, act);
+        const unsigned b0 = __ballot_sync(0xffffffffu, act && (cls & 1u));
+        const unsigned b1 = __ballot_sync(0xffffffffu, act && (cls & 2u));
+        const unsigned m0 = am & ~b0 & ~b1, m1 = b0 & ~b1, m2 = b1 & ~b0, m3 = b0 & b1;
+        const unsigned mine = cls == 0u ? m0 : (cls == 1u ? m1 : (cls == 2u ? m2 : m3));
+        const unsigned at = cls == 0u ? pos0 : (cls == 1u ? pos1 : (cls == 2u ? pos2 : pos3));
+        if (act) {
+          const unsigned pos = at + __popc(mine & lt);
+          dstK[pos] = k;
+          dstI[pos] = ix;
+        }
+        pos0 += __popc(m0); pos1 += __popc(m1); pos2 += __popc(m2); pos3 += __popc(m3);
+      }
+      __syncwarp();
+      cur ^= 1;
+      continue;
+    }
     unsigned wds[8], c[8], s = 0;
     bool single = false;
 #pragma unroll
@@ -747,13 +782,15 @@ snn_sort_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __rest
     uint32_t base = 0u;   // added back to the keys on the way out
     if (n > 32) {
       const uint32_t range = kmax - kmin;
-      const int passes = (39 - __clz(range | 1u)) >> 3;   // 8-bit digits that cover the range (1 when range < 256)
+      const int bits = 32 - __clz(range | 1u);
+      const int passes = (bits + 7) >> 3;   // 8-bit digits that cover the range (1 when range < 256)
+      const int top_bits = bits - 8 * (passes - 1);
       if (range != 0u) {
         for (int q = lane; q < 512; q += 32) sb.hist[q] = 0u;
         __syncwarp();
         rebase_and_count(sb, n, lane, kmin, passes);
         __syncwarp();
-        res = radix_sort_row_compact(sb, n, lane, passes);
+        res = radix_sort_row_compact(sb, n, lane, passes, top_bits);
         base = kmin;
       }   // else: every key is the same, index order is the sorted order
     } else {

@@ -195,3 +195,22 @@ def test_dense_unaligned_weight_and_input_pointers():
     ref = O.fc_backward(g, x, w, params, outc[:B], outc[B:], "f64")
     P.check_close(dx.cpu().numpy(), ref["dx"], "unaligned dX", abs_sum=ref["dx_abs"])
     P.check_close(dw.cpu().numpy(), ref["dw"], "unaligned dW", abs_sum=ref["dw_abs"])
+
+
+@pytest.mark.parametrize("span", [1e-4, 0.02, 0.69, 1.5, 2.2, 4.0, 11.0])
+def test_dense_forward_over_input_ranges(span):
+    """The row sort rebases its keys to the row minimum and sorts only the digits the row's range needs (a top
+    digit of one or two bits is a plain split): inputs exp(span*U[0,1)) make the range anything from a few
+    hundred key steps to many binades; a mis-sorted row shows up as a wrong causal set."""
+    import torch
+    from snntc_2023_b200 import ops
+    rng = np.random.default_rng(int(span * 1000) + 5)
+    B, I, J = 24, 200, 32
+    x = np.exp(span * rng.random((B, I))).astype(np.float32)
+    x[3, :] = x[3, 0]                      # a row of identical inputs: nothing to sort
+    x[4, ::2] = 1e5                        # half of a row never spikes
+    w = rng.normal(2.0 / I, 1.0 / np.sqrt(I), (I + 1, J)).astype(np.float32)
+    params = O.fc_params(biasvolt=1.0)
+    out = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params).cpu().numpy()
+    P.check_forward(out[:B], out[B:], O.fc_forward(x, w, params, "f32"), O.fc_forward(x, w, params, "f64"),
+                    rows=x, what="span %g" % span)
