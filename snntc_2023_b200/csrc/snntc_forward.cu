@@ -116,7 +116,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   };
 
   // one step for all JPT outputs of this lane: sign test, (rarely) exact test, then consume
-  auto step = [&](const float x, const float (&wv)[JPT]) {
+  auto step = [&](const float x, const float xprev, const float (&wv)[JPT]) {
     int q[JPT];
 #pragma unroll
     for (int m = 0; m < JPT; ++m) q[m] = __float_as_int(fmaf(-x, wsum[m], ysum[m]));
@@ -145,7 +145,6 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       wsum[m] += wv[m];
       ysum[m] = fmaf(x, wv[m], ysum[m]);
     }
-    xprev = x;
   };
 
   int k = 0;
@@ -160,7 +159,8 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       load_weights(e.y, wv[u]);
     }
 #pragma unroll
-    for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
+    for (int u = 0; u < CH; ++u) step(xs[u], u == 0 ? xprev : xs[u > 0 ? u - 1 : 0], wv[u]);
+    xprev = xs[CH - 1];   // the previous input is only read when an output is about to fire: no copy per step
     int any_live = 0;
 #pragma unroll
     for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
@@ -171,7 +171,8 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       const WalkEntry e = __ldcg(ents + k);
       float wv[JPT];
       load_weights(e.y, wv);
-      step(__uint_as_float(e.x), wv);
+      step(__uint_as_float(e.x), xprev, wv);
+      xprev = __uint_as_float(e.x);
     }
   }
 
@@ -261,7 +262,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
 
   const float* wl = w + (FULL ? jbase + 2 * lane : 0);
 
-  auto step = [&](const float x, const uint64_t (&wv)[JP]) {
+  auto step = [&](const float x, const float xprev, const uint64_t (&wv)[JP]) {
     const uint64_t x2 = pack2(x, x);
     int q[2 * JP];
 #pragma unroll
@@ -295,7 +296,6 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       nws[m] = sub2(nws[m], wv[m]);
       ys[m] = fma2(x2, wv[m], ys[m]);
     }
-    xprev = x;
   };
   const unsigned lane_off = (unsigned)jl[0];   // element offset of this lane's first pair within a weight row
   auto load_pair = [&](const float* wrow, int m) -> uint64_t {
@@ -323,7 +323,8 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       }
     }
 #pragma unroll
-    for (int u = 0; u < CH; ++u) step(xs[u], wv[u]);
+    for (int u = 0; u < CH; ++u) step(xs[u], u == 0 ? xprev : xs[u > 0 ? u - 1 : 0], wv[u]);
+    xprev = xs[CH - 1];
     int any_live = 0;
 #pragma unroll
     for (int m = 0; m < 2 * JP; ++m) any_live |= live[m];
@@ -336,7 +337,8 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       uint64_t wv[JP];
 #pragma unroll
       for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
-      step(__uint_as_float(e.x), wv);
+      step(__uint_as_float(e.x), xprev, wv);
+      xprev = __uint_as_float(e.x);
     }
   }
 
