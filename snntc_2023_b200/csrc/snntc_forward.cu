@@ -1,19 +1,21 @@
 // SNN-TC forward (SnnFc / SnnCv) for sm_100a: gather -> sort in shared memory -> sorted walk.
 //
 // Rows are dense samples or conv receptive fields (gathered straight from the NHWC image with MAX
-// outside it). Two kernels, joined by a scratch buffer of sorted keys in global memory:
-//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest are kept as
-//      32-bit sortable value bits plus a 16-bit source index in shared memory while four 8-bit digit
-//      histograms of the value bits are built;
-//   2. sort: a stable least-significant-digit radix sort by the warp (digit passes in which every key
-//      falls in one bin are skipped), O(n) per row; rows of <= 32 inputs are ranked with shuffles,
-//      rows too long for two shared-memory buffers fall back to an in-place bitonic network;
-//   3. walk (walk kernel): every warp takes (row, block of 32*JPT outputs) items; lanes span
-//      consecutive output columns so each weight-row read is one coalesced 128-byte line. The running
-//      sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the arithmetic
-//      of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is the sign of
-//      ysum - x*wsum per step, backed by the reference's exact division-free comparisons whenever it
-//      turns non-positive in any lane (see walk_row).
+// outside it). Two kernels, joined by a scratch buffer of sorted lists in global memory:
+//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest
+//      are kept as 32-bit sortable value bits plus a 16-bit source index in shared memory; conv rows find
+//      their taps through a per-CTA table, with predicated loads and no divergent branch;
+//   2. sort: the keys are rebased to the row's smallest, the 8-bit digits that the row's range needs are
+//      counted, and a stable least-significant-digit radix sort runs over those digits only (a last digit
+//      of one or two bits is a ballot split); rows of <= 32 inputs are ranked with shuffles, rows too long
+//      for two shared-memory buffers fall back to a CTA-wide in-place bitonic network;
+//   3. walk (walk kernels): every warp takes (row, block of outputs) items and walks the row's sorted list.
+//      The running sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the
+//      arithmetic of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is the
+//      sign of ysum - x*wsum per step, backed by the reference's exact division-free comparisons whenever
+//      it turns non-positive in any lane (see walk_row). Three layouts of a lane's outputs: a pair in one
+//      64-bit register (walk_row2, fan-out <= 64), 2 or 4 consecutive outputs read by one 8/16-byte load,
+//      or outputs lane + 32*m (odd fan-out, unaligned weights).
 #include "snntc_common.cuh"
 
 #include <math_constants.h>
