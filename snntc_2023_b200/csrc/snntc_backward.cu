@@ -433,12 +433,11 @@ __global__ void __launch_bounds__(kBwdThreads, 3)
 snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
               float scale, const int* __restrict__ exact_flag) {
-  // -x*s and y*s as plain tiles; -u/s as (v,v) pairs so that the two-lane FMA takes it as one 64-bit operand:
-  // columns 4t, 4t+1 of the 16 column groups t sit side by side in the first half of a row of pairs,
-  // columns 4t+2, 4t+3 in the second half, so the 16-byte reads of 8 neighbouring threads are contiguous
+  // -x*s, y*s and -u/s as plain tiles. A two-lane FMA covers two neighbouring output columns of one fan-in row,
+  // so its 64-bit operands are pairs of neighbouring columns straight out of a 16-byte read of the u tile.
   __shared__ __align__(16) float Xs[2][kRT * kTileI];
   __shared__ __align__(16) float Ys[2][kRT * kTile];
-  __shared__ __align__(16) float2 Us[2][kRT * kTile];
+  __shared__ __align__(16) float Us[2][kRT * kTile];
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
@@ -537,27 +536,23 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     if (VEC) {
       *reinterpret_cast<float4*>(&Ys[buf][ly_r * kTile + ly_c]) =
           make_float4(py[0] * sc, py[1] * sc, py[2] * sc, py[3] * sc);
-      float4* uu = reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + (ly_c >> 1)]);
-      const float u0 = pu[0] * nusc, u1 = pu[1] * nusc, u2 = pu[2] * nusc, u3 = pu[3] * nusc;
-      uu[0] = make_float4(u0, u0, u1, u1);
-      uu[kTile / 4] = make_float4(u2, u2, u3, u3);
+      *reinterpret_cast<float4*>(&Us[buf][ly_r * kTile + ly_c]) =
+          make_float4(pu[0] * nusc, pu[1] * nusc, pu[2] * nusc, pu[3] * nusc);
     } else {
-      const int slot = ((ly_c >> 1) & 1) * (kTile / 2) + 2 * (ly_c >> 2) + (ly_c & 1);
 #pragma unroll
       for (int q = 0; q < kRT / 4; ++q) {
         Ys[buf][(ly_r + 4 * q) * kTile + ly_c] = py[q] * sc;
-        const float uq = pu[q] * nusc;
-        Us[buf][(ly_r + 4 * q) * kTile + slot] = make_float2(uq, uq);
+        Us[buf][(ly_r + 4 * q) * kTile + ly_c] = pu[q] * nusc;
       }
     }
   };
 
-  // acc[a2][b] holds the sums of fan-in rows (8*ti + 2*a2, +1) and output column 4*tj + b as one 64-bit pair
-  uint64_t acc[4][4];
+  // acc[a][b2] holds the sums of fan-in row 8*ti + a and output columns 4*tj + 2*b2, +1 as one 64-bit pair
+  uint64_t acc[8][2];
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < 8; ++a)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) acc[a][b] = pack2(0.f, 0.f);
+    for (int b = 0; b < 2; ++b) acc[a][b] = pack2(0.f, 0.f);
 
   // 16 rows out of shared memory; FAST: the clamp is the saturation of the add
   auto reduce_tile = [&](int buf, auto fast_c) {
@@ -567,22 +562,21 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
       const float4 xa4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti]);
       const float4 xb4 = *reinterpret_cast<const float4*>(&Xs[buf][rr * kTileI + 8 * ti + 4]);
       const float4 y4 = *reinterpret_cast<const float4*>(&Ys[buf][rr * kTile + 4 * tj]);
-      const ulonglong2 ua = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + 2 * tj]);
-      const ulonglong2 ub = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + kTile / 2 + 2 * tj]);
+      const ulonglong2 u4 = *reinterpret_cast<const ulonglong2*>(&Us[buf][rr * kTile + 4 * tj]);
       const float nx[8] = {xa4.x, xa4.y, xa4.z, xa4.w, xb4.x, xb4.y, xb4.z, xb4.w};
       const float ys[4] = {y4.x, y4.y, y4.z, y4.w};
-      const uint64_t nu2[4] = {ua.x, ua.y, ub.x, ub.y};
+      const uint64_t nu2[2] = {u4.x, u4.y};
 #pragma unroll
-      for (int a = 0; a < 4; ++a)
+      for (int a = 0; a < 8; ++a)
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
+        for (int b = 0; b < 2; ++b) {
           float t0, t1;
           if (FAST) {
-            t0 = add_sat(ys[b], nx[2 * a]);
-            t1 = add_sat(ys[b], nx[2 * a + 1]);
+            t0 = add_sat(ys[2 * b], nx[a]);
+            t1 = add_sat(ys[2 * b + 1], nx[a]);
           } else {
-            t0 = fmaxf(ys[b] + nx[2 * a], 0.f);
-            t1 = fmaxf(ys[b] + nx[2 * a + 1], 0.f);
+            t0 = fmaxf(ys[2 * b] + nx[a], 0.f);
+            t1 = fmaxf(ys[2 * b + 1] + nx[a], 0.f);
           }
           acc[a][b] = fma2(pack2(t0, t1), nu2[b], acc[a][b]);
         }
@@ -612,14 +606,14 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 
   float* __restrict__ dst = partial + (size_t)blockIdx.z * Itot * J;
 #pragma unroll
-  for (int a = 0; a < 4; ++a)
+  for (int a = 0; a < 8; ++a)
 #pragma unroll
-    for (int b = 0; b < 4; ++b) {
+    for (int b = 0; b < 2; ++b) {
       float lo, hi;
       unpack2(acc[a][b], lo, hi);
-      const int i = i0 + 8 * ti + 2 * a, j = j0 + 4 * tj + b;
+      const int i = i0 + 8 * ti + a, j = j0 + 4 * tj + 2 * b;
       if (i < Itot && j < J) dst[(size_t)i * J + j] = lo;
-      if (i + 1 < Itot && j < J) dst[(size_t)(i + 1) * J + j] = hi;
+      if (i < Itot && j + 1 < J) dst[(size_t)i * J + j + 1] = hi;
     }
 }
 
