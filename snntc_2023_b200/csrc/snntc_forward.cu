@@ -29,6 +29,11 @@ constexpr int kFwdWarps = kFwdThreads / 32;
 
 typedef unsigned long long u64;
 
+// Index of this warp in its CTA, broadcast from lane 0: the value is the same for all 32 lanes anyway, but only
+// a shuffle from a fixed lane lets the compiler treat everything derived from it (row numbers, list lengths,
+// loop bounds) as warp-uniform, and with that it drops the divergence check in front of every warp vote.
+__device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0); }
+
 __device__ __forceinline__ float key_value(u64 e) { return sortable_to_float((uint32_t)(e >> 32)); }
 
 // ------------------------------------------------------------------------------------------- walk
@@ -853,11 +858,11 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
   float* __restrict__ inv_out = g.infer ? nullptr : out + (size_t)R * J;
   const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
-  for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
+  for (long item = (long)blockIdx.x * kFwdWarps + uniform_warp_index(); item < items; item += wstride) {
     const int rl = (int)(item / jchunks), jc = (int)(item - (long)rl * jchunks);
     const int r = row_begin + rl;
     const WalkEntry* krow = keys_g + (size_t)r * istride;
-    const int n = __ldg(nvalid_g + r);
+    const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     if (full_j)
       walk_row<JPT, (JPT >= 4 ? 4 : 8), true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
     else
@@ -878,11 +883,11 @@ snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const i
   float* __restrict__ inv_out = g.infer ? nullptr : out + (size_t)R * J;
   const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
-  for (long item = (long)blockIdx.x * kFwdWarps + (threadIdx.x >> 5); item < items; item += wstride) {
+  for (long item = (long)blockIdx.x * kFwdWarps + uniform_warp_index(); item < items; item += wstride) {
     const int rl = (int)(item / jchunks), jc = (int)(item - (long)rl * jchunks);
     const int r = row_begin + rl;
     const WalkEntry* krow = keys_g + (size_t)r * istride;
-    const int n = __ldg(nvalid_g + r);
+    const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     if (full_j)
       walk_row2<JP, (JP >= 2 ? 4 : 8), true>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
     else
