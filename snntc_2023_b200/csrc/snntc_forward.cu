@@ -729,18 +729,18 @@ __device__ __forceinline__ int radix_sort_row_compact(const SortBuffers& sb, int
         peers[q] = (q & 1) ? digit_peers(d[q], __ballot_sync(0xffffffffu, act[q])) : __match_any_sync(0xffffffffu, d[q]);
 #pragma unroll
       for (int q = 0; q < kSB; ++q) {
-        if (i0 + 32 * q < n) {   // warp-uniform
-          const unsigned before = peers[q] & lt;
-          unsigned word = 0;
-          if (act[q]) word = h[d[q]];
-          __syncwarp();
-          if (act[q] && before == 0) h[d[q]] = word + ((unsigned)__popc(peers[q]) << fs);
-          __syncwarp();
-          if (act[q]) {
-            const unsigned pos = ((word >> fs) & 0xFFFFu) + __popc(before);
-            dstK[pos] = k[q];
-            dstI[pos] = ix[q];
-          }
+        // (a batch past the end of the row has no active lane and does nothing here: no branch around the
+        // warp barriers, so that the compiler sees them in converged code)
+        const unsigned before = peers[q] & lt;
+        unsigned word = 0;
+        if (act[q]) word = h[d[q]];
+        __syncwarp();
+        if (act[q] && before == 0) h[d[q]] = word + ((unsigned)__popc(peers[q]) << fs);
+        __syncwarp();
+        if (act[q]) {
+          const unsigned pos = ((word >> fs) & 0xFFFFu) + __popc(before);
+          dstK[pos] = k[q];
+          dstI[pos] = ix[q];
         }
       }
     }
