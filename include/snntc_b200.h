@@ -192,7 +192,9 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *                                 lets a profiler time the two halves of a backward call apart
  *   snntc_profile_forward_parts   bit 0: run the sort kernel, bit 1: run the walk kernel (default 3); with 1 the
  *                                 outputs are not written -- for timing the sort alone; bits 2-3, when not 0,
- *                                 force the walk kernel's outputs per lane (1: fewest ... 3: most)
+ *                                 force the walk kernel's outputs per lane (1: fewest ... 3: most); bits 4-5, when
+ *                                 not 0, force its layout (1: output pairs, 2: outputs lane+32m, 3: consecutive
+ *                                 outputs per lane). All variants give identical bits.
  *   snntc_set_overlap             1 (default): the two independent kernels of a backward call (dX, dW) run side
  *                                 by side, dX on one library-owned auxiliary stream per device that is joined
  *                                 back with events, so the caller still sees plain stream order; 0: everything
