@@ -34,24 +34,42 @@ constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs,
 // of two is exact and (y - x) * scale stays below 1 -- an input below -MAX, a non-zero input or spike value
 // smaller than 2^-60 in magnitude, or a u that is not below 2^100 in magnitude (NaN and inf included).
 // `xin` is the whole input tensor (nx elements). The flag must be zero before the launch.
+template <bool V4>   // V4: n and nx are multiples of 4 and all pointers 16-byte aligned: 16-byte loads and stores
 __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
                              size_t n, float maxcomp, const float* __restrict__ xin, size_t nx, float maxv,
                              int* __restrict__ exact_flag) {
   const float tiny = 8.67361737988e-19f;   // 2^-60
   const float big = 1.26765060023e30f;     // 2^100
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   bool odd = false;
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
-    const float y = __ldg(out + e);
-    const float uu = (y > maxcomp) ? 0.f : __ldg(grad + e) * __ldg(out + n + e);
-    u[e] = uu;
+  auto one = [&](float y, float g, float inv) {
+    const float uu = (y > maxcomp) ? 0.f : g * inv;
     const float ya = fabsf(y);
     odd |= (ya > 0.f && ya < tiny) || !(fabsf(uu) < big);
-  }
-  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < nx; e += stride) {
-    const float xv = __ldg(xin + e);
+    return uu;
+  };
+  auto scan = [&](float xv) {
     const float xa = fabsf(xv);
     odd |= (xv < -maxv) || (xa > 0.f && xa < tiny);
+  };
+  if (V4) {
+    const float4* y4 = reinterpret_cast<const float4*>(out);
+    const float4* i4 = reinterpret_cast<const float4*>(out + n);
+    const float4* g4 = reinterpret_cast<const float4*>(grad);
+    float4* u4 = reinterpret_cast<float4*>(u);
+    for (size_t e = t0; e < n / 4; e += stride) {
+      const float4 y = __ldg(y4 + e), g = __ldg(g4 + e), iv = __ldg(i4 + e);
+      u4[e] = make_float4(one(y.x, g.x, iv.x), one(y.y, g.y, iv.y), one(y.z, g.z, iv.z), one(y.w, g.w, iv.w));
+    }
+    const float4* x4 = reinterpret_cast<const float4*>(xin);
+    for (size_t e = t0; e < nx / 4; e += stride) {
+      const float4 xv = __ldg(x4 + e);
+      scan(xv.x); scan(xv.y); scan(xv.z); scan(xv.w);
+    }
+  } else {
+    for (size_t e = t0; e < n; e += stride) u[e] = one(__ldg(out + e), __ldg(grad + e), __ldg(out + n + e));
+    for (size_t e = t0; e < nx; e += stride) scan(__ldg(xin + e));
   }
   if (odd) *exact_flag = 1;
 }
@@ -686,7 +704,10 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     if (blocks > (size_t)li.num_sms * 8) blocks = (size_t)li.num_sms * 8;
     if (cudaMemsetAsync(exact_flag, 0, sizeof(int), s) != cudaSuccess) return E_CUDA;
     const size_t nx = g.is_conv ? (size_t)g.B * g.H * g.W * g.C : (size_t)g.R * g.I;
-    snn_u_kernel<<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
+    const bool v4 = (n % 4 == 0) && (nx % 4 == 0) &&
+                    (((uintptr_t)grad | (uintptr_t)out | (uintptr_t)uv | (uintptr_t)x) & 15) == 0;
+    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
+    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
