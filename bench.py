@@ -568,7 +568,8 @@ def run_gpu_arm(args):
         total_ms = sum(v[0] for v in kinds.values()) or 1.0
         dom = max(kinds, key=lambda k: kinds[k][0])
         dms, dflops, dn = kinds[dom]
-        names = {"sort": "snn_sort_kernel", "walk": "snn_walk_kernel", "dx": "snn_dx_kernel(+snn_u_kernel)",
+        names = {"sort": "snn_sort_kernel", "walk": "snn_walk_kernel/snn_walk2_kernel",
+                 "dx": "snn_dx_wide_kernel/snn_dx_kernel(+snn_u_kernel)",
                  "dw": "snn_dw_kernel(+snn_u_kernel, reduce)"}
         traffic = None
         try:
