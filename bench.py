@@ -3,10 +3,14 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config cifar|mnist|imagenet|dense1|conv3]
     python bench.py --impl reference ...        # the reference's own CPU operators on the host cores
 
-One "step" is one train step (input encoding z=exp(t), forward, softmax-CE on -y, backward through
-SnnCvGrad/SnnFcGrad with every weight gradient written into one flat bucket, all-reduce of that
-bucket when N>1, Adam update) on one batch of synthetic input; for the single-layer configs it is
-the layer's forward plus backward on a seeded upstream gradient. Rank 0 prints ONE JSON line.
+One "step" is one train step (input encoding z=exp(t), forward, softmax-CE on -y plus the reference
+trainers' constraint cost, backward through SnnCvGrad/SnnFcGrad with every weight gradient written
+into one flat bucket, all-reduce of that bucket when N>1, Adam update) on one batch of synthetic
+input; for the single-layer configs it is the layer's forward plus backward on a seeded upstream
+gradient. Rank 0 prints ONE JSON line: the headline workload (--config, default the CIFAR-shaped
+network) with its roofline, CPU baseline and reference-GPU leg, then short runs of the other
+configurations under "configs", a small parity check against the CPU oracle under "parity", and at
+N>1 the data-parallel gradient check "dp_parity_rel_l2" and an ImageNet-shaped step.
 """
 import argparse
 import json
@@ -45,9 +49,12 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (default: the config's)")
     ap.add_argument("--cpu-sample", type=int, default=0, help="samples per CPU-baseline step (default: auto)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--profile-reps", type=int, default=3, help="timed repetitions of every kernel in the per-kernel pass")
     ap.add_argument("--no-ref-gpu", action="store_true", help="skip timing the reference's own GPU operators")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel of the step from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-extras", action="store_true", help="headline workload only: skip the short runs of the other configurations")
+    ap.add_argument("--extra-steps", type=int, default=5, help="timed steps of each extra configuration")
+    ap.add_argument("--no-parity", action="store_true", help="skip the small in-run parity check against the CPU oracle")
     return ap.parse_args()
 
 
@@ -225,6 +232,9 @@ def run_reference_arm(args):
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
+CONSTRAINT_K, CONSTRAINT_K2 = 100.0, 1e-2   # K, K2 of the reference's CIFAR trainer (snntc-cifar10.py:8-9)
+
+
 class NetWorkload:
     def __init__(self, config, batch, device, world):
         import torch
@@ -242,7 +252,10 @@ class NetWorkload:
         self.h2d_bytes = batch * int(np.prod(shape)) * 4 + batch * 8
         self.d2h_bytes = 4
         self.optimize = True
-        self.collective = True   # switched off for rank-local passes (per-kernel profiling on rank 0)
+        self.collective = True   # switched off for rank-local passes (per-kernel profiling, the gradient check on rank 0)
+
+    def host_batches(self, count, seed):
+        return host_batches(self.config, self.batch, count, seed)
 
     def stage(self, host):
         t, lab = host
@@ -255,33 +268,33 @@ class NetWorkload:
     def enable_graph(self, example_batch):
         """Capture the whole step once; later steps replay it (snntc_2023_b200.graph.GraphedStep)."""
         from snntc_2023_b200.graph import GraphedStep
-        self.graphed = GraphedStep(lambda t, lab: self._eager_step((t, lab)), list(example_batch))
+        self.graphed = GraphedStep(lambda t, lab: self.eager_step((t, lab)), list(example_batch))
 
     def step(self, dev_batch):
         if self.graphed is not None and self.optimize and (self.collective or self.world == 1):
             return self.graphed(*dev_batch)
-        return self._eager_step(dev_batch)
+        return self.eager_step(dev_batch)
 
-    def _eager_step(self, dev_batch):
-        torch = self.torch
+    def eager_step(self, dev_batch):
         t, lab = dev_batch
         z = self.train.encode(t, one_minus=False)
         loss = self.net.loss(z, lab)
-        loss.backward()
+        # the reference's train_step adds the constraint cost to the loss (snntc-mnist.py:76-80)
+        self.net.backward(loss + self.net.constraint_cost(CONSTRAINT_K, CONSTRAINT_K2))
         if self.world > 1 and self.collective:
             from snntc_2023_b200 import ddp
             ddp.allreduce_mean_(self.net.flat_grad, self.world)
         if self.optimize:
             self.opt.step()
-        return loss
+        return loss.detach()
 
 
 class LayerWorkload:
     def __init__(self, config, batch, device, world):
         import torch
-        from snntc_2023_b200 import ops
-        self.torch, self.ops = torch, ops
-        self.config, self.batch, self.device = config, batch, device
+        from snntc_2023_b200 import ops, train
+        self.torch, self.ops, self.train = torch, ops, train
+        self.config, self.batch, self.device, self.world = config, batch, device, world
         rng = np.random.default_rng(1000 * (list(CONFIGS).index(config) + 1))
         if config == "dense1":
             self.w = torch.from_numpy(rng.normal(2 / 784, 1 / 28, (784, 400)).astype(np.float32)).to(device)
@@ -295,6 +308,8 @@ class LayerWorkload:
         self.d2h_bytes = 4
         self.optimize = False
         self.collective = False
+        self.graphed = None
+        self.tap = None   # set by the per-kernel pass: the single layer's tensors, in the form ops.TAP records
 
     def host_batches(self, count, seed):
         rng = np.random.default_rng(seed)
@@ -308,17 +323,28 @@ class LayerWorkload:
     def to_device(self, pinned):
         return (pinned[0].to(self.device, non_blocking=True), pinned[1].to(self.device, non_blocking=True))
 
+    def enable_graph(self, example_batch):
+        from snntc_2023_b200.graph import GraphedStep
+        self.graphed = GraphedStep(lambda t, g: self.eager_step((t, g)), list(example_batch))
+
     def step(self, dev_batch):
-        torch, ops = self.torch, self.ops
+        if self.graphed is not None:
+            return self.graphed(*dev_batch)
+        return self.eager_step(dev_batch)
+
+    def eager_step(self, dev_batch):
+        ops = self.ops
         t, g = dev_batch
-        z = torch.exp(t)
+        z = self.train.encode(t, one_minus=False)
         if self.config == "dense1":
             out = ops.snn_fc(z, self.w, self.params)
             dx, dw, _ = ops.snn_fc_grad(g, z, self.w, self.params, out)
+            self.tap = [("fc", z, self.w, self.params, None, out, g, True)]
         else:
             out = ops.snn_cv(z, self.w, self.params, 1, 1, 32, 32)
             dx, dw, _ = ops.snn_cv_grad(g, z, self.w, self.params, out, 1, 1)
-        return dw.sum() + dx.sum()
+            self.tap = [("cv", z, self.w, self.params, (1, 1, 32, 32), out, g, True)]
+        return dw[0, 0]   # one element of the weight gradient: what the end-to-end loop reads back
 
 
 def time_region(torch, dist, world, fn, steps):
@@ -341,62 +367,78 @@ def time_region(torch, dist, world, fn, steps):
     return ms
 
 
-def profile_kernels(torch, wl, batches, steps, lib):
-    """Per-kernel CUDA-event timings of `steps` extra steps: forward calls as they are, backward calls
-    once with only the dX kernel and once with only the dW kernels enabled."""
+def tapped_layers(wl, batch):
+    """The tensors every weighted layer's backward saw in one eager step (ops.TAP), without optimiser or collective."""
     from snntc_2023_b200 import ops
+    if not hasattr(wl, "net"):
+        wl.eager_step(batch)
+        return list(wl.tap)
+    opt, coll = wl.optimize, wl.collective
+    wl.optimize, wl.collective = False, False
+    ops.TAP = []
+    try:
+        wl.eager_step(batch)
+        recs = ops.TAP
+    finally:
+        ops.TAP = None
+        wl.optimize, wl.collective = opt, coll
+    return recs
+
+
+def profile_kernels(torch, wl, batch, reps):
+    """Per-kernel CUDA-event timings: every weighted layer's operator calls are replayed on the tensors of one
+    real step (activations, upstream gradients as sparse as the pooling layers leave them), one kernel group at a
+    time through the measurement build: the list builder alone, the walk alone (lists kept in the workspace), the
+    backward with only dX, the backward with only dW (each backward call also runs the small u kernel)."""
+    from snntc_2023_b200 import _lib, ops
     agg = {}
 
-    def run(mask):
-        lib.snntc_profile_backward_parts(mask)
-        ops.Profile.records = []
-        opt, coll = wl.optimize, wl.collective
-        wl.optimize = False
-        wl.collective = False   # this pass runs on rank 0 alone: no collective may be issued here
-        for i in range(steps):
-            wl.step(batches[i % len(batches)])
+    def timed(fn):
+        fn()
         torch.cuda.synchronize()
-        wl.optimize, wl.collective = opt, coll
-        recs = ops.Profile.records
-        ops.Profile.records = None
-        lib.snntc_profile_backward_parts(3)
-        return recs
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
 
-    # forward calls are timed twice in the dX pass: the sort kernel alone (same, valid inputs), then the call
-    sort_ms = {}
-    for mask, part in ((1, "dx"), (2, "dw")):
-        ops.Profile.split_forward = (mask == 1)
-        recs = run(mask)
-        ops.Profile.split_forward = False
-        for tag, dims, e0, e1 in recs:
-            ms = e0.elapsed_time(e1)
-            if tag.endswith("forward_sort"):
-                k = (tag[:2],) + tuple(dims[:3])
-                sort_ms[k] = sort_ms.get(k, 0.0) + ms
-                continue
-            if tag.endswith("forward"):
-                if mask != 1:
-                    continue
-                key, flops = ("forward", tag[:2]) + tuple(dims[:3]), 3.0 * dims[0] * dims[1] * dims[2]
-            else:
-                if part == "dx" and not dims[3]:
-                    continue
-                key = (part, tag[:2]) + tuple(dims[:3])
-                flops = (2.0 if part == "dx" else 3.0) * dims[0] * dims[1] * dims[2]
-            a = agg.setdefault(key, [0.0, 0, flops])
+    for kind, X, W, params, geom, out, grad, need_dx in tapped_layers(wl, batch):
+        X, W, out, grad = X.detach(), W.detach(), out.detach(), grad.detach()
+        rows, J = W.shape
+        if kind == "fc":
+            R = X.shape[0]
+            ws = ops.fc_forward_workspace(R, X.shape[1], J, X.device)
+            scratch = torch.empty_like(out)
+            fwd = lambda o: ops.snn_fc(X, W, params, opts=o, workspace=ws, out=scratch)
+            bwd = lambda o, dx: ops.snn_fc_grad(grad, X, W, params, out, need_input_grad=dx, opts=o)
+        else:
+            pt, pl, Nh, Nw = geom
+            R = X.shape[0] * Nh * Nw
+            ws = ops.cv_forward_workspace(X, W, params, Nh, Nw)
+            scratch = torch.empty_like(out)
+            fwd = lambda o: ops.snn_cv(X, W, params, pt, pl, Nh, Nw, opts=o, workspace=ws, out=scratch)
+            bwd = lambda o, dx: ops.snn_cv_grad(grad, X, W, params, out, pt, pl, need_input_grad=dx, opts=o)
+        rij = float(R) * rows * J
+        parts = [("lists", lambda: fwd(_lib.options(forward_parts=1)), 0.0),
+                 ("walk", lambda: fwd(_lib.options(forward_parts=2)), 3.0 * rij),
+                 ("dw", lambda: bwd(_lib.options(backward_parts=2), False), 3.0 * rij)]
+        if need_dx:
+            parts.append(("dx", lambda: bwd(_lib.options(backward_parts=1), True), 2.0 * rij))
+        fwd(_lib.options())   # a complete forward first: the walk-only call needs this layer's lists in the workspace
+        for name, fn, flops in parts:
+            ms = timed(fn)
+            a = agg.setdefault((name, kind, R, rows, J), [0.0, 0, flops])
             a[0] += ms; a[1] += 1
-    # split the forward call into its two kernels: sort measured alone, walk = call - sort (the sort
-    # carries no flops of the 3*R*I*J count; all of them are credited to the walk)
-    for key in [k for k in agg if k[0] == "forward"]:
-        tms, n, flops = agg.pop(key)
-        s_ms = min(sort_ms.get(key[1:], 0.0), tms)
-        agg[("sort",) + key[1:]] = [s_ms, n, 0.0]
-        agg[("walk",) + key[1:]] = [max(tms - s_ms, 1e-6), n, flops]
+        del ws, scratch
     return agg
 
 
-def measure_fp32_peak(torch, lib):
+def measure_fp32_peak(torch):
     import ctypes
+    from snntc_2023_b200 import _lib
+    lib = _lib.load_measure()
     sink = torch.zeros(4, device="cuda")
     flops = ctypes.c_double(0)
     stream = torch.cuda.current_stream().cuda_stream
@@ -476,9 +518,102 @@ def time_reference_gpu(torch, wl, config, batch):
         ms = e0.elapsed_time(e1)
         total_ms += ms
         per_layer.append({"op": kind, "in": list(x.shape), "out": int(w.shape[1]), "ms": ms})
+    del rg
     return {"ms_per_step": total_ms, "value": batch / (total_ms * 1e-3), "unit": UNIT, "layers": per_layer,
             "what": "reference snn*_kernels.cu.cc compiled unmodified for sm_100a, forward+backward of every weighted "
                     "layer incl. its padding copy, temporaries and device syncs; pooling/loss/optimiser excluded"}
+
+
+def csrc_hash():
+    """Content hash of the CUDA sources: a capture under profiles/ records the hash it was taken at."""
+    import hashlib
+    d = os.path.join(ROOT, "snntc_2023_b200", "csrc")
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(d)):
+        if name.endswith((".cu", ".cuh")):
+            h.update(name.encode())
+            h.update(open(os.path.join(d, name), "rb").read())
+    return h.hexdigest()[:16]
+
+
+def in_run_parity(torch):
+    """Three small operator calls against the CPU oracle (the checker; nothing here is timed): a dense layer, a
+    hidden 3x3 conv layer of the benchmark networks and its backward. Returns the protocol's figures."""
+    import oracle as O
+    from oracle import parity as P
+    from snntc_2023_b200 import ops
+    before = len(P.REPORT)
+    x, w = P.make_inputs(1, (32, 784), (785, 400), "ref", bias=True)
+    p = O.fc_params(biasvolt=1.0)
+    out = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), p).cpu().numpy()
+    P.check_forward(out[:32], out[32:], O.fc_forward(x, w, p, "f32"), O.fc_forward(x, w, p, "f64"), rows=x, what="bench dense 784->400")
+    B, H, W, C, Kc = 2, 12, 12, 64, 128
+    x, w = P.make_inputs(2, (B, H, W, C), (9 * C + 1, Kc), "ref", bias=True)
+    p = O.cv_params(3, 3, 1, 1, "SAME", 1.0)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    outd = ops.snn_cv(xd, wd, p, 1, 1, H, W)
+    out = outd.cpu().numpy()
+    P.check_forward(out[:B], out[B:], O.cv_forward(x, w, p, "f32"), O.cv_forward(x, w, p, "f64"),
+                    rows=P.im2col_rows(x, 3, 3, 1, 1, "SAME"), what="bench conv 64->128")
+    g = np.random.default_rng(3).standard_normal((B, H, W, Kc)).astype(np.float32)
+    dx, dw, _ = ops.snn_cv_grad(torch.from_numpy(g).cuda(), xd, wd, p, outd, 1, 1)
+    ref = O.cv_backward(g, x, w, p, out[:B], out[B:], "f64")
+    P.check_close(dx.cpu().numpy(), ref["dx"], "bench conv dX", abs_sum=ref["dx_abs"])
+    P.check_close(dw.cpu().numpy(), ref["dw"], "bench conv dW", abs_sum=ref["dw_abs"])
+    s = P.summary(P.REPORT[before:])
+    s["gradients"] = "dX, dW within 1e-4*|b| + 1e-5*rms + 1e-6*sum|terms| and relative L2 <= 1e-5 of the float64 oracle"
+    return s
+
+
+def build_workload(config, batch, device, world, use_graph):
+    """Constructs the workload, stages 4 rotating input batches, warms up and (single GPU) captures the step."""
+    import torch
+    kind = CONFIGS[config][0]
+    wl = (NetWorkload if kind == "net" else LayerWorkload)(config, batch, device, world)
+    rank = int(os.environ.get("RANK", "0"))
+    nb = 4
+    seed = 1000 * (list(CONFIGS).index(config) + 1) + rank
+    pinned = [wl.stage(h) for h in wl.host_batches(nb, seed)]
+    resident = [wl.to_device(p) for p in pinned]
+    torch.cuda.synchronize()
+    for i in range(3):   # warm-up (also sizes the caching allocator)
+        wl.step(resident[i % nb])
+    torch.cuda.synchronize()
+    note = "eager launches"
+    if use_graph and world == 1:   # multi-GPU steps keep eager launches (collective inside)
+        try:
+            wl.enable_graph(resident[0])
+            for i in range(3):
+                wl.step(resident[i % nb])
+            torch.cuda.synchronize()
+            note = "whole step replayed as one CUDA graph"
+        except Exception as e:   # capture is an optimisation: fall back to eager launches and say so
+            wl.graphed = None
+            note = "eager launches (graph capture failed: %s)" % (str(e).splitlines()[0][:120],)
+            torch.cuda.synchronize()
+    return wl, pinned, resident, note
+
+
+def measure(torch, dist, lib, wl, pinned, resident, world, steps, warmup):
+    """Device-resident and end-to-end throughput of a prepared workload."""
+    nb = len(resident)
+    for i in range(max(0, warmup - 3)):
+        wl.step(resident[i % nb])
+    l0 = lib.snntc_launch_count()
+    g0 = wl.graphed.replays if wl.graphed is not None else 0
+    ms = time_region(torch, dist, world, lambda i: wl.step(resident[i % nb]), steps)
+    launches = lib.snntc_launch_count() - l0
+    if wl.graphed is not None:   # replayed kernels are not seen by the library's own counter
+        launches += (wl.graphed.replays - g0) * wl.graphed.library_launches_per_replay
+
+    # end to end: pinned host -> device every step, one value read back every step
+    def e2e_step(i):
+        b = wl.to_device(pinned[i % nb])
+        float(wl.step(b).item())
+    for i in range(2):
+        e2e_step(i)
+    ms_e2e = time_region(torch, dist, world, e2e_step, steps)
+    return ms, ms_e2e, int(launches)
 
 
 def run_gpu_arm(args):
@@ -499,56 +634,44 @@ def run_gpu_arm(args):
     lib = _lib.load()
     kind, def_batch, desc = CONFIGS[args.config]
     batch = args.batch or def_batch
-    wl = (NetWorkload if kind == "net" else LayerWorkload)(args.config, batch, device, world)
-    nb = 4
-    seed = 1000 * (list(CONFIGS).index(args.config) + 1) + rank
-    hosts = host_batches(args.config, batch, nb, seed) if kind == "net" else wl.host_batches(nb, seed)
-    pinned = [wl.stage(h) for h in hosts]
-    resident = [wl.to_device(p) for p in pinned]
-    torch.cuda.synchronize()
+    wl, pinned, resident, graph_note = build_workload(args.config, batch, device, world, not args.no_graph)
 
-    # warm-up (also sizes the caching allocator)
-    for i in range(max(args.warmup, 3)):
-        wl.step(resident[i % nb])
-    torch.cuda.synchronize()
-    graph_note = None
-    if kind == "net" and not args.no_graph and world == 1:   # multi-GPU steps keep eager launches (collective inside)
-        try:
-            wl.enable_graph(resident[0])
-            for i in range(3):
-                wl.step(resident[i % nb])
-            torch.cuda.synchronize()
-            graph_note = "whole step replayed as one CUDA graph"
-        except Exception as e:   # capture is an optimisation: fall back to eager launches and say so
-            wl.graphed = None
-            graph_note = "eager launches (graph capture failed: %s)" % (str(e).splitlines()[0][:120],)
-            torch.cuda.synchronize()
-
-    # ---- device-resident throughput
+    # ---- headline: device-resident throughput with clocks sampled during the timed region, then end to end
     sampler = ClockSampler(local) if rank == 0 else None
-    l0 = lib.snntc_launch_count()
-    g0 = wl.graphed.replays if getattr(wl, "graphed", None) is not None else 0
-    ms = time_region(torch, dist, world, lambda i: wl.step(resident[i % nb]), args.steps)
-    launches = lib.snntc_launch_count() - l0
-    if getattr(wl, "graphed", None) is not None:   # replayed kernels are not seen by the library's own counter
-        launches += (wl.graphed.replays - g0) * wl.graphed.library_launches_per_replay
+    ms, ms_e2e, launches = measure(torch, dist, lib, wl, pinned, resident, world, args.steps, max(args.warmup, 3))
     clocks = sampler.stop() if sampler else None
     value = batch * world * args.steps / (ms * 1e-3)
-
-    # ---- end to end: pinned host -> device every step, loss read back every step
-    def e2e_step(i):
-        b = wl.to_device(pinned[i % nb])
-        float(wl.step(b).item())
-    for i in range(2):
-        e2e_step(i)
-    ms_e2e = time_region(torch, dist, world, e2e_step, args.steps)
     e2e_value = batch * world * args.steps / (ms_e2e * 1e-3)
 
+    # ---- N > 1: what the all-reduce computed against the gradient of the global batch formed on rank 0 alone
+    dp_parity = None
+    if world > 1 and kind == "net":
+        from snntc_2023_b200 import ddp
+        opt = wl.optimize
+        wl.optimize = False
+        wl.eager_step(resident[0])                  # every rank: its own first batch, gradients all-reduced to the mean
+        reduced = wl.net.flat_grad.double().clone()
+        torch.cuda.synchronize()
+        if rank == 0:
+            wl.collective = False
+            acc = torch.zeros_like(reduced)
+            base = 1000 * (list(CONFIGS).index(args.config) + 1)
+            for r in range(world):                  # the other ranks' batches are regenerated from their seeds
+                b = wl.to_device(wl.stage(wl.host_batches(1, base + r)[0]))
+                wl.eager_step(b)
+                acc += wl.net.flat_grad.double()
+            acc /= world
+            dp_parity = float((reduced - acc).norm() / acc.norm())
+            wl.collective = True
+        wl.optimize = opt
+        dist.barrier()
+
     line = None
+    fp32_peak = None
     if rank == 0:
         flops_sample = algorithmic_flops_per_sample(args.config)
-        fp32_peak = measure_fp32_peak(torch, lib)
-        agg = profile_kernels(torch, wl, resident, max(1, args.profile_steps), lib)
+        fp32_peak = measure_fp32_peak(torch)
+        agg = profile_kernels(torch, wl, resident[0], max(1, args.profile_reps))
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -558,31 +681,35 @@ def run_gpu_arm(args):
         # group by kernel kind, find the dominant one
         kinds = {}
         layers = []
-        psteps = max(1, args.profile_steps)
         for key, (tms, n, flops) in sorted(agg.items()):
-            per_step = n / psteps  # launches of this shape per step
             k = kinds.setdefault(key[0], [0.0, 0.0, 0])
-            k[0] += tms / psteps; k[1] += flops * per_step; k[2] += per_step
+            k[0] += tms; k[1] += flops * n; k[2] += n
             layers.append({"kernel": key[0], "op": key[1], "R": key[2], "I": key[3], "J": key[4],
                            "ms": tms / max(n, 1), "tflops": flops / (tms / max(n, 1) * 1e-3) / 1e12})
         total_ms = sum(v[0] for v in kinds.values()) or 1.0
         dom = max(kinds, key=lambda k: kinds[k][0])
         dms, dflops, dn = kinds[dom]
-        names = {"sort": "snn_sort_kernel", "walk": "snn_walk_kernel/snn_walk2_kernel",
+        names = {"lists": "snn_pixel_runs_kernel+snn_row_runs_kernel+snn_field_lists_kernel (3x3 stride-1 conv) / snn_sort_kernel",
+                 "walk": "snn_walk_kernel/snn_walk2_kernel",
                  "dx": "snn_dx_wide_kernel/snn_dx_kernel(+snn_u_kernel)",
-                 "dw": "snn_dw_kernel(+snn_u_kernel, reduce)"}
-        traffic = None
+                 "dw": "snn_dw_skip_kernel/snn_dw_kernel(+snn_u_kernel, snn_dw_reduce_kernel)"}
+        traffic, traffic_stale = None, None
         try:
-            traffic = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(args.config, {}).get(dom)
+            tj = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+            traffic = tj.get(args.config, {}).get(dom)
+            traffic_stale = tj.get("csrc_sha16") != csrc_hash()
         except Exception:
             pass
         achieved = dflops / (dms * 1e-3) / 1e12
         roofline = {
             "bound": "fp32", "kernel": names[dom], "achieved": achieved, "peak": fp32_peak, "unit": "TFLOP/s",
-            "frac": (achieved / fp32_peak) if fp32_peak else None, "traffic": traffic,
+            "frac": (achieved / fp32_peak) if fp32_peak else None, "traffic": traffic, "traffic_stale": traffic_stale,
             "peak_source": "FMA-only probe kernel timed in this run (MEASURED_PEAKS.json holds no FP32 figure)",
             "launches_per_step": dn, "ms_per_step": dms, "share_of_kernel_time": dms / total_ms,
+            "kernel_ms_per_step": {k: v[0] for k, v in kinds.items()},
+            "kernel_frac_of_fp32_peak": {k: (v[1] / (v[0] * 1e-3) / 1e12 / fp32_peak) if (fp32_peak and v[1]) else None for k, v in kinds.items()},
             "kernel_shares": {names[k]: v[0] / total_ms for k, v in kinds.items()},
+            "how": "every kernel group of every weighted layer replayed alone on the tensors of one real step, CUDA events, mean of %d" % max(1, args.profile_reps),
             "step": {"algorithmic_tflops": flops_sample * batch / (ms / args.steps * 1e-3) / 1e12,
                      "frac_of_fp32_peak": (flops_sample * batch / (ms / args.steps * 1e-3) / 1e12 / fp32_peak) if fp32_peak else None},
             "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src, "layers": layers,
@@ -607,6 +734,12 @@ def run_gpu_arm(args):
                 ref_gpu = {"unavailable": "%s: %s" % (type(e).__name__, e)}
             if ref_gpu and "value" in ref_gpu:
                 ref_gpu["speedup_of_this_build"] = value / ref_gpu["value"]
+        parity = None
+        if not args.no_parity:
+            try:
+                parity = in_run_parity(torch)
+            except AssertionError as e:
+                parity = {"failed": str(e)[:300]}
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -614,13 +747,55 @@ def run_gpu_arm(args):
             "config": {"workload": args.config, "description": desc, "per_gpu_batch": batch, "global_batch": batch * world,
                        "parallelism": "dp%d" % world, "weights": "reference init randn*sqrt(15/fan_in), zero bias row" if kind == "net" else "N(2/I,1/I), no bias",
                        "l2": "4 rotating input batches; activations of the conv layers exceed the 126 MB L2",
+                       "objective": "softmax-CE on -y + constraint cost (K=100, K2=1e-2)" if kind == "net" else None,
                        "optimizer": "Adam (fused, flat parameter buffer)" if kind == "net" else None,
-                       "launch": graph_note or "eager launches"},
+                       "launch": graph_note},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": wl.h2d_bytes, "d2h_bytes_per_step": wl.d2h_bytes,
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
-            "reference_gpu": ref_gpu,
+            "reference_gpu": ref_gpu, "parity": parity,
         }
+        if dp_parity is not None:
+            line["dp_parity_rel_l2"] = dp_parity
+
+    # ---- the other configurations, briefly (the headline's objects are released first)
+    extras = {}
+    if not args.no_extras:
+        del wl, pinned, resident
+        torch.cuda.empty_cache()
+        extra_names = [c for c in ("conv3", "dense1", "mnist", "imagenet") if c != args.config] if world == 1 else \
+                      [c for c in ("imagenet",) if c != args.config]
+        for cfg in extra_names:
+            try:
+                b = CONFIGS[cfg][1]
+                w2, p2, r2, note2 = build_workload(cfg, b, device, world, not args.no_graph)
+                ms2, ms2_e2e, l2 = measure(torch, dist, lib, w2, p2, r2, world, args.extra_steps, 3)
+                entry = {"value": b * world * args.extra_steps / (ms2 * 1e-3), "unit": UNIT, "ms_per_step": ms2 / args.extra_steps,
+                         "per_gpu_batch": b, "steps": args.extra_steps, "launch": note2, "gpu_launches": l2,
+                         "e2e": {"value": b * world * args.extra_steps / (ms2_e2e * 1e-3), "h2d_bytes_per_step": w2.h2d_bytes,
+                                 "d2h_bytes_per_step": w2.d2h_bytes}}
+                if rank == 0:
+                    fs = algorithmic_flops_per_sample(cfg)
+                    entry["step_frac_of_fp32"] = (fs * b / (ms2 / args.extra_steps * 1e-3) / 1e12 / fp32_peak) if fp32_peak else None
+                    if world == 1 and not args.no_ref_gpu:
+                        try:
+                            rg = time_reference_gpu(torch, w2, cfg, b)
+                            if rg and "value" in rg:
+                                entry["reference_gpu_ms_per_step"] = rg["ms_per_step"]
+                                entry["reference_gpu_speedup"] = entry["value"] / rg["value"]
+                        except Exception as e:
+                            entry["reference_gpu_speedup"] = None
+                            entry["reference_gpu_error"] = "%s: %s" % (type(e).__name__, str(e)[:120])
+                extras[cfg] = entry
+                del w2, p2, r2
+                torch.cuda.empty_cache()
+            except Exception as e:
+                extras[cfg] = {"failed": "%s: %s" % (type(e).__name__, str(e)[:200])}
+                if world > 1:
+                    raise
+        if line is not None:
+            line["configs"] = extras
+
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

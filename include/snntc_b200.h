@@ -107,12 +107,14 @@ SNNTC_API int snntc_cv_backward(const float* grad, const float* x_nhwc, const fl
  * pads with 1e5 and calls -MaxPool2D(-x) in TensorFlow (SNN_TC_Modules.py:216-246). Here: window
  * minimum over the UNPADDED NHWC input with out-of-image taps reading `padvalue`; arg[B,Nh,Nw,C]
  * receives the flat input index of each winner (first minimum in (kh,kw) order, -1 for padding) and
- * drives the backward, which zero-fills dx[n_in] and adds gy[o] at arg[o].
+ * drives the backward: every input element sums gy over the windows it won, in window order (a gather --
+ * no atomics, so overlapping windows give the same bits every run); dx[B,H,W,C] is written in full.
  */
 SNNTC_API int snntc_minpool_forward(const float* x_nhwc, float* y, int* arg, int B, int H, int W, int C,
                                     int Kh, int Kw, int Sh, int Sw, int pad_top, int pad_left, int Nh, int Nw,
                                     float padvalue, void* stream);
-SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx, size_t n_out, size_t n_in,
+SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx, int B, int H, int W, int C,
+                                     int Kh, int Kw, int Sh, int Sw, int pad_top, int pad_left, int Nh, int Nw,
                                      void* stream);
 
 /* ------------------------------------------------------------------------------------------------
@@ -121,11 +123,16 @@ SNNTC_API int snntc_minpool_backward(const float* gy, const int* arg, float* dx,
  * (snntc_fc_forward_workspace_bytes / snntc_cv_forward_workspace_bytes) and values as snntc_fc_forward /
  * snntc_cv_forward. The reference has one operator for training and evaluation (snntc-mnist.py:88-94 calls
  * the training forward with training=False); this is its serving-side half.
+ *   khist (device, may be null): fan_in + 2 counters, fan_in without the bias row (Kh*Kw*C for the convolution).
+ *   khist[k] is incremented for every output that fired after consuming k inputs (its causal-set size; the bias
+ *   input is not counted), khist[fan_in + 1] for every output that did not fire. The caller zeroes it. The
+ *   reference has no such output: its kernel only breaks out of the walk (snntc/snnfc_kernels.cu.cc:45-48); the
+ *   histogram says how early the outputs of a layer fire, i.e. what stopping early can save.
  */
-SNNTC_API int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ,
+SNNTC_API int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ, int* khist,
                              int B, int I, int w_rows, int J,
                              void* workspace, size_t workspace_bytes, void* stream);
-SNNTC_API int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+SNNTC_API int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out, int* khist,
                              int B, int H, int W, int C, int w_rows, int Kc,
                              int pad_top, int pad_left, int Nh, int Nw,
                              void* workspace, size_t workspace_bytes, void* stream);
@@ -166,17 +173,22 @@ SNNTC_API int snntc_sgdm_step(float* w, const float* g, float* vel, size_t n, fl
  * For callers that have no way to allocate device memory when the dense backward runs (an operator
  * plugin that is handed only its declared inputs and outputs, a loop with a fixed memory plan, a
  * process whose device memory belongs to another pool): same arguments and results as
- * snntc_fc_backward, minus the workspace. The partial weight-gradient tiles go to a fixed array of
- * SNNTC_NOALLOC_SCRATCH_BYTES that is part of the library image, so every GPU that loads the library
- * holds that much memory until the process exits. The call allocates and frees nothing.
- *   - Problems whose partial tiles need more than the array (snntc_fc_backward_workspace_bytes() >
+ * snntc_fc_backward, minus the workspace. Everything snntc_fc_backward keeps in its workspace -- the
+ * per-output factor u[B,J] = grad/(sum w - threshold), the range flag of the weight-gradient kernel and
+ * that kernel's partial tiles -- goes to a fixed array of SNNTC_NOALLOC_SCRATCH_BYTES that is part of the
+ * library image, so every GPU that loads the library holds that much memory until the process exits.
+ * The call allocates and frees nothing, on the device or through the CUDA runtime: it also keeps all its
+ * kernels on `stream` (the regular entry point may run two of them side by side on a library-owned
+ * auxiliary stream, which is created on first use).
+ *   - Problems that need more than the array (snntc_fc_backward_workspace_bytes() >
  *     snntc_noalloc_scratch_bytes()) are refused with SNNTC_E_WORKSPACE; nothing is launched.
  *   - The first call on each device resolves the array's device address and reads two device
  *     attributes; make that first call outside any stream capture, with the device current.
  *   - All calls on a device share the one array. Calls whose kernels can overlap on the GPU (two
- *     streams, two host threads) race on it: run them one after the other on one stream, or order
- *     the streams with events. The array keeps the previous call's contents; the kernels overwrite
- *     every element they later read, so no clearing is needed between calls.
+ *     streams, two host threads) race on it -- on u and the flag even when the problem is too small to
+ *     have partial tiles: run them one after the other on one stream, or order the streams with events.
+ *     The array keeps the previous call's contents; the kernels write every element before they read
+ *     it, so no clearing is needed between calls.
  */
 #define SNNTC_NOALLOC_SCRATCH_BYTES (8u << 20)
 SNNTC_API size_t snntc_noalloc_scratch_bytes(void);
@@ -186,28 +198,53 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
                                         int B, int I, int w_rows, int J, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
- * Measurement helpers (no counterpart in the reference).
- *   snntc_launch_count            kernels launched by this library since it was loaded
- *   snntc_profile_backward_parts  bit 0: run the dX kernel, bit 1: run the dW kernels (default 3);
- *                                 lets a profiler time the two halves of a backward call apart
- *   snntc_profile_forward_parts   bit 0: run the sort kernel, bit 1: run the walk kernel (default 3); with 1 the
- *                                 outputs are not written -- for timing the sort alone; bits 2-3, when not 0,
- *                                 force the walk kernel's outputs per lane (1: fewest ... 3: most); bits 4-5, when
- *                                 not 0, force its layout (1: output pairs, 2: outputs lane+32m, 3: consecutive
- *                                 outputs per lane). All variants give identical bits.
- *   snntc_set_overlap             1 (default): the two independent kernels of a backward call (dX, dW) run side
- *                                 by side, dX on one library-owned auxiliary stream per device that is joined
- *                                 back with events, so the caller still sees plain stream order; 0: everything
- *                                 runs on the caller's stream
- *   snntc_fp32_probe              queues `ctas` CTAs of 256 threads running `iters` rounds of 8
- *                                 independent FMAs each and reports the flop count: timed by the
- *                                 caller, it gives the FP32 issue ceiling the kernels are judged against
+ * Library-wide helpers (no counterpart in the reference).
+ *   snntc_launch_count   kernels launched by this library since it was loaded
+ *   snntc_set_overlap    1 (default): the two independent kernels of a backward call (dX, dW) run side by side,
+ *                        dX on a library-owned auxiliary stream that is joined back with events, so the caller
+ *                        still sees plain stream order; 0: everything runs on the caller's stream. The setting
+ *                        only chooses between two schedules of the same kernels. Entry points may be called
+ *                        from several host threads and on several streams at once: the library keeps no state
+ *                        between calls apart from per-device caches behind a lock.
  */
 SNNTC_API unsigned long long snntc_launch_count(void);
-SNNTC_API void snntc_profile_backward_parts(int mask);
-SNNTC_API void snntc_profile_forward_parts(int mask);
 SNNTC_API void snntc_set_overlap(int on);
+
+#ifdef SNNTC_MEASURE
+/* ------------------------------------------------------------------------------------------------
+ * Measurement build only (libsnntc_b200_measure.so, compiled with -DSNNTC_MEASURE; the default library does
+ * not export these). The four operators with the kernel choice of THE CALL given explicitly, so that a
+ * benchmark can time the kernels of an operator apart and a test can check the variants against each other:
+ *   opts7 = { forward_parts   bit 0: build the sorted lists, bit 1: walk them (default 3; without bit 1 the
+ *                             output is not written),
+ *             walk_layout     0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane,
+ *             walk_outputs    0 auto, 1..4: 1, 2, 4, 8 outputs per lane,
+ *             list_builder    0 auto, 1 per-row radix sort, 2 per-pixel sort + merges,
+ *             backward_parts  bit 0: dX, bit 1: dW (default 3),
+ *             dw_kernel       0 auto, 1 dense register tile, 2 row-skipping kernel,
+ *             overlap         -1 library setting, 0 one stream, 1 dX beside dW }
+ * A null opts7 means the defaults. All variants of a kernel give the same values (the walk variants the same
+ * bits). snntc_fp32_probe queues `ctas` CTAs of 256 threads running `iters` rounds of 8 independent FMAs each
+ * and reports the flop count: timed by the caller, it gives the FP32 issue ceiling the kernels are judged against.
+ */
+SNNTC_API int snntc_measure_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
+                                       int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
+                                       const int* opts7, void* stream);
+SNNTC_API int snntc_measure_fc_backward(const float* grad_2BJ, const float* x, const float* w,
+                                        const float* params6_host, const float* out_2BJ, float* dx, float* dw,
+                                        float* dparams6, int B, int I, int w_rows, int J,
+                                        void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
+SNNTC_API int snntc_measure_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                                       int B, int H, int W, int C, int w_rows, int Kc,
+                                       int pad_top, int pad_left, int Nh, int Nw,
+                                       void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
+SNNTC_API int snntc_measure_cv_backward(const float* grad, const float* x_nhwc, const float* w,
+                                        const float* params12_host, const float* out, float* dx, float* dw,
+                                        float* dparams12, int B, int H, int W, int C, int w_rows, int Kc,
+                                        int pad_top, int pad_left, int Nh, int Nw,
+                                        void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
 SNNTC_API int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream);
+#endif /* SNNTC_MEASURE */
 
 #ifdef __cplusplus
 }

@@ -10,7 +10,7 @@ Two artefacts, both git-ignored:
                                          used to time the reference's GPU kernels on a B200 and as a
                                          second parity check
 
-Run:  python oracle/build.py [--reference-root DIR]
+Run:  python oracle/build.py [--reference-root DIR]   (default: $SNNTC_REFERENCE_ROOT, else ../reference)
 """
 import argparse
 import os
@@ -24,6 +24,15 @@ REF_SO = os.path.join(REF_DIR, "libsnntc_ref_cpu.so")
 REF_SOURCES = ["snnfc_kernels.cc", "snnfcgrad_kernels.cc", "snncv_kernels.cc", "snncvgrad_kernels.cc"]
 REF_GPU_SO = os.path.join(REF_DIR, "libsnntc_ref_gpu.so")
 REF_GPU_SOURCES = ["snnfc_kernels.cu.cc", "snnfcgrad_kernels.cu.cc", "snncv_kernels.cu.cc", "snncvgrad_kernels.cu.cc"]
+
+
+def default_reference_root():
+    """Where the reference checkout is looked for: $SNNTC_REFERENCE_ROOT, else a directory named `reference`
+    beside this repository."""
+    env = os.environ.get("SNNTC_REFERENCE_ROOT")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def _newer(target, deps):
@@ -43,9 +52,9 @@ def build_oracle(force=False):
     return ORACLE_SO
 
 
-def build_ref(reference_root="/root/reference", force=False):
+def build_ref(reference_root=None, force=False):
     """Compile the reference CPU operators where they lie. Returns the .so path or None."""
-    src_dir = os.path.join(reference_root, "snntc")
+    src_dir = os.path.join(reference_root or default_reference_root(), "snntc")
     srcs = [os.path.join(src_dir, s) for s in REF_SOURCES]
     if not all(os.path.exists(s) for s in srcs):
         return REF_SO if os.path.exists(REF_SO) else None
@@ -61,10 +70,10 @@ def build_ref(reference_root="/root/reference", force=False):
     return REF_SO
 
 
-def build_ref_gpu(reference_root="/root/reference", force=False):
+def build_ref_gpu(reference_root=None, force=False):
     """Compile the reference GPU operators where they lie (nvcc, sm_100a). Returns the .so path or None."""
     import shutil
-    src_dir = os.path.join(reference_root, "snntc")
+    src_dir = os.path.join(reference_root or default_reference_root(), "snntc")
     srcs = [os.path.join(src_dir, s) for s in REF_GPU_SOURCES]
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not all(os.path.exists(s) for s in srcs) or not os.path.exists(nvcc):
@@ -90,7 +99,7 @@ def build_ref_gpu(reference_root="/root/reference", force=False):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference-root", default="/root/reference")
+    ap.add_argument("--reference-root", default=None, help="default: $SNNTC_REFERENCE_ROOT or ../reference")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     print(build_oracle(a.force))

@@ -13,8 +13,6 @@ import torch.nn.functional as F
 
 from . import ops
 
-Check_Dim = False
-
 
 def init_weight(in_size=1, out_size=1, bias_volt=1.0, init_param=15.0):
     """randn * sqrt(init_param / in_size), plus a zero bias row appended last (reference :19-25)."""
@@ -50,7 +48,7 @@ class SNN_dense(torch.nn.Module):
         if tuple(weight.shape) != (self.in_size, self.out_size):
             raise ValueError("weight must have shape [%d, %d], got %s" % (self.in_size, self.out_size, tuple(weight.shape)))
         self.weight = torch.nn.Parameter(weight)
-        self.grad_sink = None  # optional slice of a flat gradient bucket (see ddp.FlatGradBucket)
+        self.grad_sink = None  # optional slice of a flat gradient bucket (nets.SnnNet sets it): dW is written there
 
     def forward(self, X):
         return ops.snn_fc_layer(X, self.weight, self.Params, self.grad_sink)

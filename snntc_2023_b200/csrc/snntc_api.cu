@@ -12,59 +12,94 @@
 
 namespace snntc {
 static std::atomic<unsigned long long> g_launches{0};
-static std::atomic<int> g_backward_parts{3};
-static std::atomic<int> g_forward_parts{3};
 static std::atomic<int> g_overlap{1};
-static std::mutex g_aux_mutex;
-static AuxStream g_aux[64];
-static int g_aux_state[64];   // 0 = not tried, 1 = ready, -1 = creation failed
 
-AuxStream* aux_stream() {
-  if (!g_overlap.load(std::memory_order_relaxed)) return nullptr;
+// Auxiliary streams: kAuxSlots per device, handed out round robin. The mutex serialises slot creation and every
+// (record, wait) pair, so that an event is never re-recorded between its record and the wait that refers to it.
+constexpr int kAuxSlots = 4;
+constexpr int kMaxDevices = 64;
+struct AuxPool {
+  int state;   // 0 = not tried, 1 = ready, -1 = creation failed
+  unsigned next;
+  AuxSlot slot[kAuxSlots];
+};
+static std::mutex g_aux_mutex;
+static AuxPool g_aux[kMaxDevices];
+
+AuxSlot* aux_acquire(int overlap_option) {
+  const int overlap = overlap_option < 0 ? g_overlap.load(std::memory_order_relaxed) : overlap_option;
+  if (!overlap) return nullptr;
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
   std::lock_guard<std::mutex> lock(g_aux_mutex);
-  if (g_aux_state[dev] == 0) {
-    AuxStream& a = g_aux[dev];
-    bool ok = cudaStreamCreateWithFlags(&a.stream, cudaStreamNonBlocking) == cudaSuccess;
-    ok = ok && cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) == cudaSuccess;
-    for (int i = 0; ok && i < 8; ++i) ok = cudaEventCreateWithFlags(&a.join[i], cudaEventDisableTiming) == cudaSuccess;
-    g_aux_state[dev] = ok ? 1 : -1;
+  AuxPool& p = g_aux[dev];
+  if (p.state == 0) {
+    bool ok = true;
+    for (int i = 0; ok && i < kAuxSlots; ++i) {
+      ok = cudaStreamCreateWithFlags(&p.slot[i].stream, cudaStreamNonBlocking) == cudaSuccess;
+      ok = ok && cudaEventCreateWithFlags(&p.slot[i].fork, cudaEventDisableTiming) == cudaSuccess;
+      ok = ok && cudaEventCreateWithFlags(&p.slot[i].join, cudaEventDisableTiming) == cudaSuccess;
+    }
+    p.state = ok ? 1 : -1;
     if (!ok) cudaGetLastError();
   }
-  return g_aux_state[dev] == 1 ? &g_aux[dev] : nullptr;
+  if (p.state != 1) return nullptr;
+  return &p.slot[p.next++ % kAuxSlots];
+}
+
+cudaError_t aux_fork(AuxSlot* a, cudaStream_t caller) {
+  std::lock_guard<std::mutex> lock(g_aux_mutex);
+  cudaError_t e = cudaEventRecord(a->fork, caller);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(a->stream, a->fork, 0);
+  return e;
+}
+
+cudaError_t aux_join(AuxSlot* a, cudaStream_t caller) {
+  std::lock_guard<std::mutex> lock(g_aux_mutex);
+  cudaError_t e = cudaEventRecord(a->join, a->stream);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(caller, a->join, 0);
+  return e;
 }
 
 void count_launch(int n) { g_launches.fetch_add((unsigned long long)n, std::memory_order_relaxed); }
-int backward_parts() { return g_backward_parts.load(std::memory_order_relaxed); }
-int forward_parts() { return g_forward_parts.load(std::memory_order_relaxed); }
-}  // namespace snntc
 
-namespace {
-
-thread_local char g_cuda_err[256] = "";
+static thread_local char g_cuda_err[256] = "";
 
 void note_cuda_error(cudaError_t e) {
   if (e == cudaSuccess) return;
   strncpy(g_cuda_err, cudaGetErrorString(e), sizeof(g_cuda_err) - 1);
   g_cuda_err[sizeof(g_cuda_err) - 1] = 0;
 }
+}  // namespace snntc
+
+namespace {
+
+using snntc::note_cuda_error;
 
 struct DevCache { int ready; snntc::LaunchInfo li; };
-DevCache g_dev[64];
+std::mutex g_dev_mutex;
+DevCache g_dev[snntc::kMaxDevices];
 
 int launch_info(snntc::LaunchInfo* li) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
-  if (dev >= 0 && dev < 64 && g_dev[dev].ready) { *li = g_dev[dev].li; return SNNTC_OK; }
+  const bool cached = dev >= 0 && dev < snntc::kMaxDevices;
+  if (cached) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (g_dev[dev].ready) { *li = g_dev[dev].li; return SNNTC_OK; }
+  }
   int sms = 0, smem = 0;
   e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
   if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
   li->num_sms = sms;
   li->max_smem_optin = smem;
-  if (dev >= 0 && dev < 64) { g_dev[dev].li = *li; g_dev[dev].ready = 1; }
+  if (cached) {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    g_dev[dev].li = *li;
+    g_dev[dev].ready = 1;
+  }
   return SNNTC_OK;
 }
 
@@ -129,17 +164,19 @@ int finish(int rc) {
   return rc;
 }
 
-int run_forward(const snntc::Geometry& g, const float* x, const float* w, float* out, void* ws, size_t wsb, void* stream) {
+int run_forward(const snntc::Geometry& g, const float* x, const float* w, float* out, void* ws, size_t wsb,
+                const snntc::Options& opt, void* stream) {
   snntc::LaunchInfo li;
   int rc = launch_info(&li);
   if (rc) return rc;
   rc = check_ws(ws, wsb, snntc::forward_workspace_bytes(g));
   if (rc) return rc;
-  return finish(snntc::launch_forward(g, x, w, out, ws, wsb, li, (cudaStream_t)stream));
+  return finish(snntc::launch_forward(g, x, w, out, ws, wsb, li, opt, (cudaStream_t)stream));
 }
 
 int run_backward(const snntc::Geometry& g, const float* grad, const float* x, const float* w, const float* out,
-                 float* dx, float* dw, float* dparams, int nparams, void* ws, size_t wsb, void* stream) {
+                 float* dx, float* dw, float* dparams, int nparams, void* ws, size_t wsb,
+                 const snntc::Options& opt, void* stream) {
   snntc::LaunchInfo li;
   int rc = launch_info(&li);
   if (rc) return rc;
@@ -149,7 +186,61 @@ int run_backward(const snntc::Geometry& g, const float* grad, const float* x, co
     cudaError_t e = cudaMemsetAsync(dparams, 0, sizeof(float) * nparams, (cudaStream_t)stream);
     if (e != cudaSuccess) { note_cuda_error(e); return SNNTC_E_CUDA; }
   }
-  return finish(snntc::launch_backward(g, grad, x, w, out, dx, dw, ws, wsb, li, (cudaStream_t)stream));
+  return finish(snntc::launch_backward(g, grad, x, w, out, dx, dw, ws, wsb, li, opt, (cudaStream_t)stream));
+}
+
+// Geometry of a workspace query: only what the planning reads. Strides are taken as 1 so that the query covers
+// the list builder that needs the most scratch whatever the stride of the call turns out to be.
+snntc::Geometry cv_query_geometry(int B, int H, int W, int C, int w_rows_or_I, int Kc, int Kh, int Kw, int Nh, int Nw) {
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.is_conv = 1; g.B = B; g.H = H; g.W = W; g.C = C; g.J = Kc; g.Kh = Kh; g.Kw = Kw; g.Nh = Nh; g.Nw = Nw;
+  g.Sh = g.Sw = 1;
+  g.I = w_rows_or_I; g.R = B * Nh * Nw;
+  return g;
+}
+
+int fc_forward_impl(const float* x, const float* w, const float* params6_host, float* out, int B, int I, int w_rows,
+                    int J, int infer, int* khist, void* ws, size_t wsb, const snntc::Options& opt, void* stream) {
+  if (!x || !w || !out) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
+  if (rc) return rc;
+  g.infer = infer;
+  g.khist = infer ? khist : nullptr;
+  return run_forward(g, x, w, out, ws, wsb, opt, stream);
+}
+
+int cv_forward_impl(const float* x, const float* w, const float* params12_host, float* out, int B, int H, int W, int C,
+                    int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw, int infer, int* khist,
+                    void* ws, size_t wsb, const snntc::Options& opt, void* stream) {
+  if (!x || !w || !out) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
+  if (rc) return rc;
+  g.infer = infer;
+  g.khist = infer ? khist : nullptr;
+  return run_forward(g, x, w, out, ws, wsb, opt, stream);
+}
+
+int fc_backward_impl(const float* grad, const float* x, const float* w, const float* params6_host, const float* out,
+                     float* dx, float* dw, float* dparams6, int B, int I, int w_rows, int J,
+                     void* ws, size_t wsb, const snntc::Options& opt, void* stream) {
+  if (!grad || !x || !w || !out || !dw) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
+  if (rc) return rc;
+  return run_backward(g, grad, x, w, out, dx, dw, dparams6, 6, ws, wsb, opt, stream);
+}
+
+int cv_backward_impl(const float* grad, const float* x, const float* w, const float* params12_host, const float* out,
+                     float* dx, float* dw, float* dparams12, int B, int H, int W, int C, int w_rows, int Kc,
+                     int pad_top, int pad_left, int Nh, int Nw, void* ws, size_t wsb, const snntc::Options& opt,
+                     void* stream) {
+  if (!grad || !x || !w || !out || !dw) return SNNTC_E_NULL;
+  snntc::Geometry g;
+  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
+  if (rc) return rc;
+  return run_backward(g, grad, x, w, out, dx, dw, dparams12, 12, ws, wsb, opt, stream);
 }
 
 }  // namespace
@@ -171,19 +262,99 @@ const char* snntc_status_string(int status) {
   }
 }
 
-const char* snntc_last_cuda_error(void) { return g_cuda_err; }
+const char* snntc_last_cuda_error(void) { return snntc::g_cuda_err; }
 
-const char* snntc_version(void) { return "snntc_b200 0.1 sm_100a"; }
+const char* snntc_version(void) {
+#ifdef SNNTC_MEASURE
+  return "snntc_b200 0.2 sm_100a (measurement build)";
+#else
+  return "snntc_b200 0.2 sm_100a";
+#endif
+}
 
 unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std::memory_order_relaxed); }
 
 void snntc_set_overlap(int on) { snntc::g_overlap.store(on ? 1 : 0, std::memory_order_relaxed); }
 
-void snntc_profile_forward_parts(int mask) { snntc::g_forward_parts.store(mask & 63, std::memory_order_relaxed); }
+size_t snntc_fc_forward_workspace_bytes(int B, int I, int J) {
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.R = B; g.I = I; g.J = J;
+  return snntc::forward_workspace_bytes(g);
+}
 
-void snntc_profile_backward_parts(int mask) { snntc::g_backward_parts.store(mask & 3, std::memory_order_relaxed); }
+int snntc_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
+                     int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  return fc_forward_impl(x, w, params6_host, out_2BJ, B, I, w_rows, J, 0, nullptr, workspace, workspace_bytes,
+                         snntc::Options(), stream);
+}
 
+int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ, int* khist,
+                   int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  return fc_forward_impl(x, w, params6_host, out_BJ, B, I, w_rows, J, 1, khist, workspace, workspace_bytes,
+                         snntc::Options(), stream);
+}
+
+size_t snntc_fc_backward_workspace_bytes(int B, int I, int w_rows, int J) {
+  if (B <= 0 || I <= 0 || J <= 0 || w_rows < I) return 0;
+  snntc::Geometry g; memset(&g, 0, sizeof(g));
+  g.R = B; g.I = I; g.J = J; g.has_bias = w_rows > I ? 1 : 0;
+  return snntc::backward_workspace_bytes(g, launch_info_or_default());
+}
+
+int snntc_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
+                      const float* out_2BJ, float* dx, float* dw, float* dparams6,
+                      int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
+  return fc_backward_impl(grad_2BJ, x, w, params6_host, out_2BJ, dx, dw, dparams6, B, I, w_rows, J, workspace,
+                          workspace_bytes, snntc::Options(), stream);
+}
+
+size_t snntc_cv_forward_workspace_bytes(int B, int H, int W, int C, int Kc, int Kh, int Kw, int Nh, int Nw) {
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || Kc <= 0 || Kh <= 0 || Kw <= 0 || Nh <= 0 || Nw <= 0) return 0;
+  return snntc::forward_workspace_bytes(cv_query_geometry(B, H, W, C, Kh * Kw * C, Kc, Kh, Kw, Nh, Nw));
+}
+
+int snntc_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                     int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  return cv_forward_impl(x_nhwc, w, params12_host, out, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, 0, nullptr,
+                         workspace, workspace_bytes, snntc::Options(), stream);
+}
+
+int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out, int* khist,
+                   int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+  return cv_forward_impl(x_nhwc, w, params12_host, out, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, 1, khist,
+                         workspace, workspace_bytes, snntc::Options(), stream);
+}
+
+size_t snntc_cv_backward_workspace_bytes(int B, int H, int W, int C, int w_rows, int Kc, int Nh, int Nw) {
+  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || Kc <= 0 || w_rows <= 0 || Nh <= 0 || Nw <= 0) return 0;
+  // planning depends only on the total weight rows: they stand in for the fan-in, bias row included
+  return snntc::backward_workspace_bytes(cv_query_geometry(B, H, W, C, w_rows, Kc, 0, 0, Nh, Nw), launch_info_or_default());
+}
+
+int snntc_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
+                      const float* out, float* dx, float* dw, float* dparams12,
+                      int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  return cv_backward_impl(grad, x_nhwc, w, params12_host, out, dx, dw, dparams12, B, H, W, C, w_rows, Kc, pad_top,
+                          pad_left, Nh, Nw, workspace, workspace_bytes, snntc::Options(), stream);
+}
+
+#ifdef SNNTC_MEASURE
+/* ---- measurement build only: the same operators with the kernel choice of the call given explicitly.
+ * opts7 = {forward_parts, walk_layout, walk_outputs, list_builder, backward_parts, dw_kernel, overlap}
+ * (see snntc::Options); a null pointer means the defaults. Nothing here is process-wide state. */
 namespace {
+snntc::Options options_from(const int* o) {
+  snntc::Options opt;
+  if (o) {
+    opt.forward_parts = o[0]; opt.walk_layout = o[1]; opt.walk_outputs = o[2]; opt.list_builder = o[3];
+    opt.backward_parts = o[4]; opt.dw_kernel = o[5]; opt.overlap = o[6];
+  }
+  return opt;
+}
+
 // independent FMA chains, nothing else: the FP32 issue ceiling a masked-FMA kernel is judged against
 __global__ void __launch_bounds__(256) fp32_probe_kernel(float* sink, int iters, float a, float b) {
   float v[8];
@@ -200,6 +371,36 @@ __global__ void __launch_bounds__(256) fp32_probe_kernel(float* sink, int iters,
 }
 }  // namespace
 
+int snntc_measure_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
+                             int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
+                             const int* opts7, void* stream) {
+  return fc_forward_impl(x, w, params6_host, out_2BJ, B, I, w_rows, J, 0, nullptr, workspace, workspace_bytes,
+                         options_from(opts7), stream);
+}
+
+int snntc_measure_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
+                              const float* out_2BJ, float* dx, float* dw, float* dparams6,
+                              int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
+                              const int* opts7, void* stream) {
+  return fc_backward_impl(grad_2BJ, x, w, params6_host, out_2BJ, dx, dw, dparams6, B, I, w_rows, J, workspace,
+                          workspace_bytes, options_from(opts7), stream);
+}
+
+int snntc_measure_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
+                             int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                             void* workspace, size_t workspace_bytes, const int* opts7, void* stream) {
+  return cv_forward_impl(x_nhwc, w, params12_host, out, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, 0, nullptr,
+                         workspace, workspace_bytes, options_from(opts7), stream);
+}
+
+int snntc_measure_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
+                              const float* out, float* dx, float* dw, float* dparams12,
+                              int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
+                              void* workspace, size_t workspace_bytes, const int* opts7, void* stream) {
+  return cv_backward_impl(grad, x_nhwc, w, params12_host, out, dx, dw, dparams12, B, H, W, C, w_rows, Kc, pad_top,
+                          pad_left, Nh, Nw, workspace, workspace_bytes, options_from(opts7), stream);
+}
+
 int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream) {
   if (!sink || !flops_out) return SNNTC_E_NULL;
   if (iters <= 0 || ctas <= 0) return SNNTC_E_SHAPE;
@@ -208,95 +409,6 @@ int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* 
   *flops_out = 2.0 * 8.0 * (double)iters * 256.0 * (double)ctas;
   return cudaGetLastError() == cudaSuccess ? SNNTC_OK : SNNTC_E_CUDA;
 }
-
-size_t snntc_fc_forward_workspace_bytes(int B, int I, int J) {
-  snntc::Geometry g; memset(&g, 0, sizeof(g));
-  g.R = B; g.I = I; g.J = J;
-  return snntc::forward_workspace_bytes(g);
-}
-
-int snntc_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
-                     int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x || !w || !out_2BJ) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
-  if (rc) return rc;
-  return run_forward(g, x, w, out_2BJ, workspace, workspace_bytes, stream);
-}
-
-int snntc_fc_infer(const float* x, const float* w, const float* params6_host, float* out_BJ,
-                   int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x || !w || !out_BJ) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
-  if (rc) return rc;
-  g.infer = 1;
-  return run_forward(g, x, w, out_BJ, workspace, workspace_bytes, stream);
-}
-
-size_t snntc_fc_backward_workspace_bytes(int B, int I, int w_rows, int J) {
-  if (B <= 0 || I <= 0 || J <= 0 || w_rows < I) return 0;
-  snntc::Geometry g; memset(&g, 0, sizeof(g));
-  g.R = B; g.I = I; g.J = J; g.has_bias = w_rows > I ? 1 : 0;
-  return snntc::backward_workspace_bytes(g, launch_info_or_default());
-}
-
-int snntc_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
-                      const float* out_2BJ, float* dx, float* dw, float* dparams6,
-                      int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!grad_2BJ || !x || !w || !out_2BJ || !dw) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = fc_geometry(params6_host, B, I, w_rows, J, &g);
-  if (rc) return rc;
-  return run_backward(g, grad_2BJ, x, w, out_2BJ, dx, dw, dparams6, 6, workspace, workspace_bytes, stream);
-}
-
-size_t snntc_cv_forward_workspace_bytes(int B, int H, int W, int C, int Kc, int Kh, int Kw, int Nh, int Nw) {
-  snntc::Geometry g; memset(&g, 0, sizeof(g));
-  g.is_conv = 1; g.B = B; g.H = H; g.W = W; g.C = C; g.J = Kc; g.Kh = Kh; g.Kw = Kw; g.Nh = Nh; g.Nw = Nw;
-  g.I = Kh * Kw * C; g.R = B * Nh * Nw;
-  return snntc::forward_workspace_bytes(g);
-}
-
-int snntc_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
-                     int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
-                     void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x_nhwc || !w || !out) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
-  if (rc) return rc;
-  return run_forward(g, x_nhwc, w, out, workspace, workspace_bytes, stream);
-}
-
-int snntc_cv_infer(const float* x_nhwc, const float* w, const float* params12_host, float* out,
-                   int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
-                   void* workspace, size_t workspace_bytes, void* stream) {
-  if (!x_nhwc || !w || !out) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
-  if (rc) return rc;
-  g.infer = 1;
-  return run_forward(g, x_nhwc, w, out, workspace, workspace_bytes, stream);
-}
-
-size_t snntc_cv_backward_workspace_bytes(int B, int H, int W, int C, int w_rows, int Kc, int Nh, int Nw) {
-  if (B <= 0 || H <= 0 || W <= 0 || C <= 0 || Kc <= 0 || w_rows <= 0 || Nh <= 0 || Nw <= 0) return 0;
-  snntc::Geometry g; memset(&g, 0, sizeof(g));
-  g.is_conv = 1; g.B = B; g.H = H; g.W = W; g.C = C; g.J = Kc; g.Nh = Nh; g.Nw = Nw;
-  g.I = w_rows; g.has_bias = 0;   // planning depends only on the total weight rows
-  g.R = B * Nh * Nw;
-  return snntc::backward_workspace_bytes(g, launch_info_or_default());
-}
-
-int snntc_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
-                      const float* out, float* dx, float* dw, float* dparams12,
-                      int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
-                      void* workspace, size_t workspace_bytes, void* stream) {
-  if (!grad || !x_nhwc || !w || !out || !dw) return SNNTC_E_NULL;
-  snntc::Geometry g;
-  int rc = cv_geometry(params12_host, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, &g);
-  if (rc) return rc;
-  return run_backward(g, grad, x_nhwc, w, out, dx, dw, dparams12, 12, workspace, workspace_bytes, stream);
-}
+#endif  /* SNNTC_MEASURE */
 
 }  // extern "C"

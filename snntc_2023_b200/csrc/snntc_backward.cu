@@ -34,10 +34,16 @@ constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs,
 // of two is exact and (y - x) * scale stays below 1 -- an input below -MAX, a non-zero input or spike value
 // smaller than 2^-60 in magnitude, or a u that is not below 2^100 in magnitude (NaN and inf included).
 // `xin` is the whole input tensor (nx elements). The flag must be zero before the launch.
+// It also fills the twelve constants behind the flag that snn_dw_skip_kernel copies in place of inputs that are
+// not there: MAX x4, {biasvolt, MAX, MAX, MAX}, 0 x4.
 template <bool V4>   // V4: n and nx are multiples of 4 and all pointers 16-byte aligned: 16-byte loads and stores
 __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
                              size_t n, float maxcomp, const float* __restrict__ xin, size_t nx, float maxv,
-                             int* __restrict__ exact_flag) {
+                             int* __restrict__ exact_flag, float* __restrict__ consts, float biasvolt) {
+  if (blockIdx.x == 0 && threadIdx.x < 12) {
+    const int t = threadIdx.x;
+    consts[t] = t < 4 ? maxv : (t == 4 ? biasvolt : (t < 8 ? maxv : 0.f));
+  }
   const float tiny = 8.67361737988e-19f;   // 2^-60
   const float big = 1.26765060023e30f;     // 2^100
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -670,9 +676,11 @@ static size_t u_bytes(const Geometry& g) { return (((size_t)g.R * g.J * sizeof(f
 constexpr size_t kFlagBytes = 256;
 
 // The power of two s with 2*MAX*s <= 1/2 (so that (y - x)*s < 1 whenever y <= MAX and x >= -MAX), or 1 when
-// MAX or the bias input are outside the range in which the scaled inner loop of snn_dw_kernel is exact.
+// MAX or the bias input are outside the range in which the scaled inner loop of the dW kernels is exact: with
+// MAX <= 2^24, s >= 2^-27, so that -u/s stays finite for |u| < 2^100 and y*s, x*s stay normal numbers for
+// magnitudes down to 2^-60 (the bounds snn_u_kernel checks on the tensors).
 static float dw_scale(const Geometry& g) {
-  if (!(g.maxv > 0.f) || !(g.maxv < 1e27f)) return 1.0f;
+  if (!(g.maxv > 0.f) || !(g.maxv <= 16777216.0f)) return 1.0f;
   if (g.has_bias) {
     const float ba = fabsf(g.biasvolt);
     if (g.biasvolt < -g.maxv || (ba > 0.f && ba < 8.67361737988e-19f)) return 1.0f;
@@ -682,19 +690,38 @@ static float dw_scale(const Geometry& g) {
   return ldexpf(1.0f, -(e + 2));  // 2*maxv*s < 2^(e+1) * 2^-(e+2) = 1/2
 }
 
+// Where the row-skipping dW kernel is used: conv layers it supports with enough rows and fan-in to fill its tiles.
+static bool want_dw_skip(const Geometry& g, const Options& opt) {
+  if (opt.dw_kernel == 1) return false;
+  if (!g.is_conv || (g.C & 3) != 0 || (g.J & 3) != 0) return false;
+  if (opt.dw_kernel == 2) return true;
+  return g.R >= 2048 && g.I >= 128;
+}
+
 size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
+  const size_t plane = (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
   const DwPlan p = plan_dw(g, li);
-  const size_t part = p.splits <= 1 ? 0 : (size_t)p.splits * (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
+  size_t part = p.splits <= 1 ? 0 : (size_t)p.splits * plane;
+  Options any;
+  any.dw_kernel = 2;
+  if (want_dw_skip(g, any)) {   // sized for either dW kernel: which one runs also depends on pointer alignment
+    int rps = 0;
+    const size_t skip = (size_t)dw_skip_splits(g, li, &rps) * plane;
+    if (skip > part) part = skip;
+  }
   return u_bytes(g) + kFlagBytes + part;
 }
 
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
-                    float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, cudaStream_t s) {
+                    float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, const Options& opt,
+                    cudaStream_t s) {
   const int Itot = g.I + g.has_bias;
-  const int parts = backward_parts();
-  if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return -5;
+  const int parts = opt.backward_parts;
+  if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return E_WORKSPACE;
   float* uv = static_cast<float*>(ws);
   int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + u_bytes(g));
+  float* consts = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + 64);
+  float* planes = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + kFlagBytes);
   // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
   const bool vec = (g.J % 4 == 0) && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)uv) & 15) == 0 &&
                    (((size_t)g.R * g.J) % 4 == 0);
@@ -706,19 +733,19 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const size_t nx = g.is_conv ? (size_t)g.B * g.H * g.W * g.C : (size_t)g.R * g.I;
     const bool v4 = (n % 4 == 0) && (nx % 4 == 0) &&
                     (((uintptr_t)grad | (uintptr_t)out | (uintptr_t)uv | (uintptr_t)x) & 15) == 0;
-    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
-    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
+    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, consts, g.biasvolt);
+    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, consts, g.biasvolt);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
-  // dX and dW only share read-only inputs: run dX on the auxiliary stream beside dW when both are wanted
-  AuxStream* aux = (dx && parts == 3 && (long)g.R * g.J >= 65536) ? aux_stream() : nullptr;
+  // dX and dW only share read-only inputs: run dX on an auxiliary stream beside dW when both are wanted
+  AuxSlot* aux = (dx && parts == 3 && (long)g.R * g.J >= 65536) ? aux_acquire(opt.overlap) : nullptr;
   cudaStream_t sdx = s;
   if (aux) {
-    if (cudaEventRecord(aux->fork, s) != cudaSuccess || cudaStreamWaitEvent(aux->stream, aux->fork, 0) != cudaSuccess)
-      return E_CUDA;
+    if (aux_fork(aux, s) != cudaSuccess) return E_CUDA;
     sdx = aux->stream;
   }
+  int rc = OK;
   if (dx && (parts & 1)) {
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
@@ -732,29 +759,47 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
       snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
     }
     count_launch();
-    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
-    if (aux && cudaEventRecord(aux->join[0], aux->stream) != cudaSuccess) return E_CUDA;
+    if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
   }
-  if (!(parts & 2)) return OK;
-  const DwPlan p = plan_dw(g, li);
-  float* partial = dw;
-  if (p.splits > 1) partial = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + kFlagBytes);
-  dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTileI - 1) / kTileI, p.splits);
-  const float scale = dw_scale(g);
-  if (vec) snn_dw_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
-  else snn_dw_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
-  count_launch();
-  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
-  if (p.splits > 1) {
+  if (rc == OK && (parts & 2)) {
+    const float scale = dw_scale(g);
     const size_t n = (size_t)Itot * g.J;
-    int blocks = (int)((n + 255) / 256);
-    if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
-    snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, p.splits);
-    count_launch();
-    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+    int splits = 1;
+    float* partial = dw;
+    if (want_dw_skip(g, opt) && dw_skip_supported(g, x, uv, out)) {
+      int rps = 0;
+      splits = dw_skip_splits(g, li, &rps);
+      partial = planes;   // always reduced from the workspace: its tiles are stored 16 bytes at a time
+      rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, consts, li, s);
+      splits = splits < 1 ? 1 : splits;
+      if (rc == OK) {
+        int blocks = (int)((n + 255) / 256);
+        if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
+        snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, splits);
+        count_launch();
+        if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+      }
+    } else {
+      const DwPlan p = plan_dw(g, li);
+      if (p.splits > 1) partial = planes;
+      dim3 grid((g.J + kTile - 1) / kTile, (Itot + kTileI - 1) / kTileI, p.splits);
+      if (vec) snn_dw_kernel<true><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
+      else snn_dw_kernel<false><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, p.rows_per_split, scale, exact_flag);
+      count_launch();
+      if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+      if (rc == OK && p.splits > 1) {
+        int blocks = (int)((n + 255) / 256);
+        if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
+        snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, p.splits);
+        count_launch();
+        if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+      }
+    }
   }
-  if (aux && cudaStreamWaitEvent(s, aux->join[0], 0) != cudaSuccess) return E_CUDA;
-  return OK;
+  // the auxiliary stream is joined on every path, so that an error return never leaves it forked (a stream
+  // capture in progress would otherwise be invalid)
+  if (aux && aux_join(aux, s) != cudaSuccess && rc == OK) rc = E_CUDA;
+  return rc;
 }
 
 }  // namespace snntc

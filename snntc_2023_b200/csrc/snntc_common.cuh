@@ -20,6 +20,9 @@ struct Geometry {
   int B, H, W, C, Kh, Kw, Sh, Sw, pad_top, pad_left, Nh, Nw;
   // forward only: 1 = inference (the output is [R,J] spike values; 1/(sum w - theta) is not written)
   int infer;
+  // inference only, may be null: I+2 counters. khist[k] += 1 for every output that fired after consuming k inputs
+  // (the bias input is not counted), khist[I+1] += 1 for every output that did not fire.
+  int* khist;
 };
 
 struct LaunchInfo {
@@ -27,37 +30,75 @@ struct LaunchInfo {
   int max_smem_optin;  // bytes of dynamic shared memory one CTA may opt in to
 };
 
+// Per-call choices among kernels that compute the same thing. The default (all zero / all parts) is the
+// library's own choice; anything else comes from the measurement entry points of a -DSNNTC_MEASURE build
+// and from the tests that check the variants against each other. Nothing here is process-wide state.
+struct Options {
+  int forward_parts = 3;    // bit 0: build the sorted lists, bit 1: walk them
+  int walk_layout = 0;      // 0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane
+  int walk_outputs = 0;     // 0 auto, 1..4: 1, 2, 4, 8 outputs per lane (pairs layout: 2 only)
+  int list_builder = 0;     // 0 auto, 1 per-row radix sort, 2 per-pixel sort + merges (3x3 stride-1 conv only)
+  int backward_parts = 3;   // bit 0: dX, bit 1: dW
+  int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0)
+  int overlap = -1;         // -1 library setting (snntc_set_overlap), 0 one stream, 1 dX beside dW
+};
+
 // number of kernels this library has launched since it was loaded (read by snntc_launch_count)
 void count_launch(int n = 1);
-// profiling aid: bit 0 = run the dX kernel, bit 1 = run the dW kernels (default 3)
-int backward_parts();
-// profiling aid: bit 0 = run the sort kernel, bit 1 = run the walk kernel (default 3)
-int forward_parts();
+// remembers the text of a CUDA runtime error for snntc_last_cuda_error() (per host thread)
+void note_cuda_error(cudaError_t e);
 
-// One auxiliary stream and a few events per device, created on first use and kept for the life of the
-// process. Kernels of one call that do not depend on each other (dX and dW) are forked onto it and
-// joined back into the caller's stream with events, so the caller still sees ordinary stream order. Returns nullptr when the
-// resources cannot be created or overlap is switched off (snntc_set_overlap(0)): callers then run
-// everything on the one stream.
-struct AuxStream {
+// A few auxiliary streams per device, each with its own fork/join events, created on first use and kept for
+// the life of the process. Kernels of one call that do not depend on each other (dX and dW) are forked onto
+// one of them and joined back into the caller's stream with events, so the caller still sees ordinary stream
+// order. Slots are handed out round robin; an event record and the wait that refers to it are issued under one
+// lock, so calls from several host threads (or one thread alternating streams) never wait on each other's
+// fork points. aux_acquire returns nullptr when the resources cannot be created or overlap is off: callers then
+// run everything on the one stream.
+struct AuxSlot {
   cudaStream_t stream;
-  cudaEvent_t fork;       // recorded on the caller's stream, waited on by the auxiliary stream
-  cudaEvent_t join[8];    // recorded on the auxiliary stream, waited on by the caller's stream
+  cudaEvent_t fork;   // recorded on the caller's stream, waited on by the auxiliary stream
+  cudaEvent_t join;   // recorded on the auxiliary stream, waited on by the caller's stream
 };
-AuxStream* aux_stream();
+AuxSlot* aux_acquire(int overlap_option);
+cudaError_t aux_fork(AuxSlot* a, cudaStream_t caller);   // a->stream waits for everything queued on caller so far
+cudaError_t aux_join(AuxSlot* a, cudaStream_t caller);   // caller waits for everything queued on a->stream so far
 
 // status codes mirrored from include/snntc_b200.h
-enum { OK = 0, E_UNSUPPORTED = -6, E_CUDA = -7 };
+enum { OK = 0, E_WORKSPACE = -5, E_UNSUPPORTED = -6, E_CUDA = -7 };
+
+// Entry of a sorted list handed from the list builders to the walk kernels: x = input value (float bits),
+// y = element offset of its weight row (source index * J).
+typedef uint2 WalkEntry;
 
 // ---- forward ---------------------------------------------------------------------------------
 size_t forward_workspace_bytes(const Geometry& g);
 int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void* ws, size_t ws_bytes,
-                   const LaunchInfo& li, cudaStream_t s);
+                   const LaunchInfo& li, const Options& opt, cudaStream_t s);
+
+// Sorted lists of a 3x3 (any Kh x Kw up to 3x3 here), stride-1 convolution by per-pixel sorting and two levels of
+// merging (snntc_lists.cu). merge_lists_supported says whether the geometry qualifies, merge_lists_shape_ok the same
+// without looking at the strides (what a workspace query knows); merge_lists_bytes is the scratch it needs beyond
+// the lists themselves.
+bool merge_lists_shape_ok(const Geometry& g);
+bool merge_lists_supported(const Geometry& g);
+size_t merge_lists_bytes(const Geometry& g);
+int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
+                       void* scratch, const LaunchInfo& li, cudaStream_t s);
 
 // ---- backward --------------------------------------------------------------------------------
 size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li);
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
-                    float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, cudaStream_t s);
+                    float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, const Options& opt,
+                    cudaStream_t s);
+
+// dW by a kernel that skips the (row, output) pairs that did not fire (snntc_dw_skip.cu); conv layers whose
+// channel count is a multiple of 4. `consts` points at {MAX, biasvolt, 0, 0} in device memory (16-byte aligned).
+bool dw_skip_supported(const Geometry& g, const float* x, const float* uv, const float* out);
+int dw_skip_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split);
+int launch_dw_skip(const Geometry& g, const float* uv, const float* x, const float* out, float* partial,
+                   int splits, int rows_per_split, float scale, const int* exact_flag, const float* consts,
+                   const LaunchInfo& li, cudaStream_t s);
 
 // monotone map float bits -> unsigned so that an unsigned compare orders like the float compare
 __host__ __device__ __forceinline__ uint32_t float_to_sortable(float f) {

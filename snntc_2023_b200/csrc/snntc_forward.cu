@@ -37,9 +37,6 @@ __device__ __forceinline__ int uniform_warp_index() { return __shfl_sync(0xfffff
 __device__ __forceinline__ float key_value(u64 e) { return sortable_to_float((uint32_t)(e >> 32)); }
 
 // ------------------------------------------------------------------------------------------- walk
-// Entry of the sorted list handed from the sort kernel to the walk kernel: x = input value,
-// y = element offset of its weight row (source index * J).
-typedef uint2 WalkEntry;
 
 // "ysum/wsum > c" without a division, as the reference evaluates it after consuming input c
 // (snntc/snnfc_kernels.cu.cc:53-55)
@@ -55,23 +52,36 @@ __device__ __forceinline__ bool ratio_le(float ysum, float wsum, float c) {
   return ya <= c * wa;
 }
 
-__device__ __forceinline__ int or3(int a, int b, int c) {
-  int r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xFE;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+// smallest of three floats in one instruction (three-input min of sm_100); a NaN operand is ignored
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+  float r;
+  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
 
-// One warp walks one row for 32*JPT outputs (lane + 32*m). Let q_k = ysum - x_k*wsum be taken just
-// before input k is consumed. The reference fires at step k when "ysum/wsum > previous input" and
-// "ysum/wsum <= x_k", i.e. sign(wsum)*q_{k-1} > 0 >= sign(wsum)*q_k (q_{k-1} re-evaluated with the sums
-// of step k, which leaves its value unchanged). q starts positive (theta*x_0, or theta*biasvolt with
-// bias) and moves by -(x_k - x_{k-1})*wsum per step, so a change of sign can only happen in the
-// direction that sign(wsum) allows: the FIRST fire is simply the first k with q_k <= 0. The loop
-// therefore computes one extra FMA per output and step (q, with its exact sign), ORs the sign bits and
-// takes one warp vote; only when some lane sees q <= 0 does the warp evaluate the reference's own
-// rounded, division-free tests for the outputs concerned, so the decision is the reference's. An output
-// whose q is non-positive but which the reference test did not fire (possible only when q is within an
-// ulp of zero) keeps being tested exactly at every following step.
+// Number of list entries whose input value lies strictly below y: the causal-set size of an output that fired
+// at y (every consumed input is below the spike value, every other one is not). Binary search, one thread.
+__device__ __forceinline__ int entries_below(const WalkEntry* __restrict__ ents, int n, float y) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__uint_as_float(__ldcg(ents + mid).x) < y) lo = mid + 1; else hi = mid;
+  }
+  return lo;
+}
+
+// One warp walks one row for 32*JPT outputs. Let q_k = ysum - x_k*wsum be taken just before input k is
+// consumed. The reference fires at step k when "ysum/wsum > previous input" and "ysum/wsum <= x_k", i.e.
+// sign(wsum)*q_{k-1} > 0 >= sign(wsum)*q_k (q_{k-1} re-evaluated with the sums of step k, which leaves its
+// value unchanged). With a positive denominator -- the only case in which an output of sorted inputs at or
+// above the bias input can fire -- that is the first k with q_k <= 0. The loop therefore computes one extra FMA
+// per output and step (q, with its exact sign), takes the smallest q of the lane and one warp vote; only when
+// some lane sees q <= 0 does the warp evaluate the reference's own rounded, division-free tests
+// (snntc/snnfc_kernels.cu.cc:46-55) for its live outputs, so the decision is the reference's, an exact tie
+// (q == 0) included. An output whose q is not positive but which the reference test did not fire -- q within an
+// ulp of zero, or a NEGATIVE denominator, which inputs below the bias input can produce and for which the
+// reference fires on the way back up through zero -- makes the lane "sticky": the exact tests run again at
+// the next step whatever q is, until no live output of the lane is in that state any more.
 template <int JPT, int CH, bool FULL, bool VECW>
 __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
@@ -83,7 +93,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   int livemask[JPT];
 #pragma unroll
   for (int m = 0; m < JPT; ++m) {
-    // VECW: a lane owns JPT consecutive outputs and reads them with one 8- or 16-byte load (J % JPT == 0,
+    // VECW: a lane owns JPT consecutive outputs and reads them with 8- or 16-byte loads (J % JPT == 0,
     // so a lane is wholly inside or wholly outside the row); otherwise outputs lane + 32*m, 4-byte loads
     const int j = VECW ? jbase + JPT * lane + m : jbase + lane + 32 * m;
     jok[m] = FULL || j < J;
@@ -102,19 +112,25 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   // Without bias the sums start at (-theta, 0), for which "ysum/wsum > c" is false for every c >= 0, so the
   // first step needs no special case; with bias the previous input is the bias input itself.
   float xprev = g.has_bias ? g.biasvolt : 0.f;
+  float sticky = CUDART_INF_F;   // -1 while some live output of this lane must be tested exactly at the next step
 
   const float* wl = w + (VECW ? jl[0] : (FULL ? jbase + lane : 0));
-  // VECW: one load per step, addressed by a 32-bit element offset from the (uniform) weight base -- measured
-  // faster than a 64-bit per-lane pointer plus the entry's offset
+  // VECW: addressed by a 32-bit element offset from the (uniform) weight base, widened before the scaling to
+  // bytes -- measured faster than a 64-bit per-lane pointer plus the entry's offset
   const unsigned lane_off = (unsigned)jl[0];
   const char* wbase = reinterpret_cast<const char*>(w);
   auto load_weights = [&](unsigned eoff, float (&wv)[JPT]) {
     const float* wrow = wl + eoff;
-    if (VECW && JPT == 4) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(wbase + (size_t)((eoff + lane_off) * 4u)));
+    if constexpr (VECW && JPT == 8) {
+      const float4* p4 = reinterpret_cast<const float4*>(wbase + (size_t)(eoff + lane_off) * 4u);
+      const float4 v = __ldg(p4), v2 = __ldg(p4 + 1);
       wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
-    } else if (VECW && JPT == 2) {
-      const float2 v = __ldg(reinterpret_cast<const float2*>(wbase + (size_t)((eoff + lane_off) * 4u)));
+      wv[4] = v2.x; wv[5] = v2.y; wv[6] = v2.z; wv[7] = v2.w;
+    } else if constexpr (VECW && JPT == 4) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(wbase + (size_t)(eoff + lane_off) * 4u));
+      wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
+    } else if constexpr (VECW && JPT == 2) {
+      const float2 v = __ldg(reinterpret_cast<const float2*>(wbase + (size_t)(eoff + lane_off) * 4u));
       wv[0] = v.x; wv[1] = v.y;
     } else {
 #pragma unroll
@@ -124,28 +140,34 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
 
   // one step for all JPT outputs of this lane: sign test, (rarely) exact test, then consume
   auto step = [&](const float x, const float xprev, const float (&wv)[JPT]) {
-    int q[JPT];
+    float q[JPT];
 #pragma unroll
-    for (int m = 0; m < JPT; ++m) q[m] = __float_as_int(fmaf(-x, wsum[m], ysum[m]));
-    int orall = q[0];
-    if (JPT == 2) orall |= q[1];
-    if (JPT == 4) orall = or3(or3(q[0], q[1], q[2]), q[3], 0);
-    if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
-      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive (usually one
-      // of the lane's outputs in one lane: skip the others with a warp-uniform test each)
+    for (int m = 0; m < JPT; ++m) q[m] = fmaf(-x, wsum[m], ysum[m]);
+    float qmin;
+    if constexpr (JPT == 1) qmin = fminf(q[0], sticky);
+    else if constexpr (JPT == 2) qmin = fmin3(q[0], q[1], sticky);
+    else if constexpr (JPT == 4) qmin = fmin3(fmin3(q[0], q[1], q[2]), q[3], sticky);
+    else qmin = fmin3(fmin3(q[0], q[1], q[2]), fmin3(q[3], q[4], q[5]), fmin3(q[6], q[7], sticky));
+    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0.f), 0)) {
+      // rare path: the reference's own rounded comparisons for the live outputs concerned (usually one of the
+      // lane's outputs in one lane: skip the others with a warp-uniform test each)
+      bool again = false;
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
-        if (JPT > 1 && !__any_sync(0xffffffffu, q[m] < 0)) continue;
-        const bool fire = (q[m] < 0) & (livemask[m] != 0) & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
+        if (JPT > 1 && !__any_sync(0xffffffffu, (q[m] <= 0.f) | (sticky < 0.f))) continue;
+        const bool live = livemask[m] != 0;
+        const bool fire = live & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
         if (fire) {
           livemask[m] = 0;  // spike lies in (previous input, x]: keep the sums aside ...
           wfin[m] = wsum[m];
           yfin[m] = ysum[m];
-          // ... and park the running ones where q can never be negative again: with wsum = -inf,
+          // ... and park the running ones where q can never be non-positive again: with wsum = -inf,
           // q = ysum + x*inf = +inf at every later step
           wsum[m] = -CUDART_INF_F;
         }
+        again |= live & !fire & (q[m] <= 0.f);
       }
+      sticky = again ? -1.f : CUDART_INF_F;
     }
 #pragma unroll
     for (int m = 0; m < JPT; ++m) {
@@ -202,6 +224,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       const int j = VECW ? jbase + JPT * lane + m : jbase + lane + 32 * m;
       y_row[j] = yv;
       if (inv_row != nullptr) inv_row[j] = iv;
+      if (g.khist != nullptr) atomicAdd(g.khist + (yv < g.maxv ? entries_below(ents, nvalid, yv) : g.I + 1), 1);
     }
   }
 }
@@ -216,9 +239,6 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 }
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ void unpack2i(uint64_t v, int& lo, int& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
 }
 __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   uint64_t r;
@@ -269,16 +289,19 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
 
   const float* wl = w + (FULL ? jbase + 2 * lane : 0);
 
+  float sticky = CUDART_INF_F;   // -1 while some live output of this lane must be tested exactly at the next step
   auto step = [&](const float x, const float xprev, const uint64_t (&wv)[JP]) {
     const uint64_t x2 = pack2(x, x);
-    int q[2 * JP];
+    float q[2 * JP];
 #pragma unroll
-    for (int m = 0; m < JP; ++m) unpack2i(fma2(x2, nws[m], ys[m]), q[2 * m], q[2 * m + 1]);
-    int orall = q[0] | q[1];
-    if (JP == 2) orall = or3(orall, q[2], q[3]);
-    if (JP == 4) orall = or3(or3(orall, q[2], q[3]), or3(q[4], q[5], q[6]), q[7]);
-    if (__builtin_expect(__any_sync(0xffffffffu, orall < 0), 0)) {
-      // rare path: the reference's own rounded comparisons for the outputs whose q is not positive
+    for (int m = 0; m < JP; ++m) unpack2(fma2(x2, nws[m], ys[m]), q[2 * m], q[2 * m + 1]);
+    float qmin;
+    if constexpr (JP == 1) qmin = fmin3(q[0], q[1], sticky);
+    else if constexpr (JP == 2) qmin = fmin3(fmin3(q[0], q[1], q[2]), q[3], sticky);
+    else qmin = fmin3(fmin3(q[0], q[1], q[2]), fmin3(q[3], q[4], q[5]), fmin3(q[6], q[7], sticky));
+    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0.f), 0)) {
+      // rare path: the reference's own rounded comparisons for the live outputs (see walk_row)
+      bool again = false;
 #pragma unroll
       for (int m = 0; m < JP; ++m) {
         float n[2], y[2];
@@ -287,16 +310,19 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const float wsum = 0.f - n[h];   // not -n: an exactly cancelled sum must read +0 as in the scalar walk
-          const bool fire = (q[2 * m + h] < 0) & (live[2 * m + h] != 0) & ratio_gt(y[h], wsum, xprev) & ratio_le(y[h], wsum, x);
+          const bool lv = live[2 * m + h] != 0;
+          const bool fire = lv & ratio_gt(y[h], wsum, xprev) & ratio_le(y[h], wsum, x);
           if (fire) {
             live[2 * m + h] = 0;   // spike lies in (previous input, x]: keep the sums aside ...
             wfin[2 * m + h] = wsum;
             yfin[2 * m + h] = y[h];
             n[h] = CUDART_INF_F;   // ... and park the running weight sum where q stays +inf
           }
+          again |= lv & !fire & (q[2 * m + h] <= 0.f);
         }
         nws[m] = pack2(n[0], n[1]);
       }
+      sticky = again ? -1.f : CUDART_INF_F;
     }
 #pragma unroll
     for (int m = 0; m < JP; ++m) {
@@ -322,7 +348,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
         // one pair per lane: a 32-bit element offset from the (uniform) weight base measured faster than a
         // 64-bit per-lane pointer plus the entry's offset
         wv[u][0] = __ldg(reinterpret_cast<const unsigned long long*>(
-            reinterpret_cast<const char*>(w) + (size_t)((e.y + lane_off) * 4u)));
+            reinterpret_cast<const char*>(w) + (size_t)(e.y + lane_off) * 4u));
       } else {
         const float* wrow = wl + e.y;
 #pragma unroll
@@ -373,6 +399,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
         const int j = jbase + 2 * lane + 64 * m + h;
         y_row[j] = yv;
         if (inv_row != nullptr) inv_row[j] = iv;
+        if (g.khist != nullptr) atomicAdd(g.khist + (yv < g.maxv ? entries_below(ents, nvalid, yv) : g.I + 1), 1);
       }
     }
   }
@@ -858,15 +885,16 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
   float* __restrict__ inv_out = g.infer ? nullptr : out + (size_t)R * J;
   const long items = (long)(row_end - row_begin) * jchunks;
   const long wstride = (long)gridDim.x * kFwdWarps;
+  constexpr int CH = JPT >= 8 ? 2 : (JPT >= 4 ? 4 : 8);
   for (long item = (long)blockIdx.x * kFwdWarps + uniform_warp_index(); item < items; item += wstride) {
     const int rl = (int)(item / jchunks), jc = (int)(item - (long)rl * jchunks);
     const int r = row_begin + rl;
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     if (full_j)
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row<JPT, CH, true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
     else
-      walk_row<JPT, (JPT >= 4 ? 4 : 8), false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row<JPT, CH, false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
   }
 }
 
@@ -898,6 +926,7 @@ snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const i
 int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of keys start 16-byte aligned
 
 size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
+size_t nvalid_bytes(const Geometry& g) { return ((size_t)g.R * sizeof(int) + 255) & ~(size_t)255; }
 
 template <int JPT, bool VECW>
 int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
@@ -925,25 +954,34 @@ int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
 
+// Lists of a conv layer are built by per-pixel sorting and merging when the geometry allows it and the row
+// sort would sort every input pixel several times over (3x3 stride 1: nine times).
+bool use_merge_lists(const Geometry& g, const Options& opt) {
+  if (opt.list_builder == 1 || !merge_lists_supported(g)) return false;
+  return true;
+}
+
 }  // namespace
 
 size_t forward_workspace_bytes(const Geometry& g) {
-  return keys_bytes(g) + (((size_t)g.R * sizeof(int) + 15) & ~(size_t)15);
+  // sorted lists, their lengths, and (conv layers that qualify) the scratch of the merging list builder
+  return keys_bytes(g) + nvalid_bytes(g) + (merge_lists_shape_ok(g) ? merge_lists_bytes(g) : 0);
 }
 
 int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void* ws, size_t ws_bytes,
-                   const LaunchInfo& li, cudaStream_t s) {
-  if (!ws || ws_bytes < forward_workspace_bytes(g)) return -5;
+                   const LaunchInfo& li, const Options& opt, cudaStream_t s) {
+  if (!ws || ws_bytes < forward_workspace_bytes(g)) return E_WORKSPACE;
   WalkEntry* keys_g = static_cast<WalkEntry*>(ws);
   int* nvalid_g = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + keys_bytes(g));
+  void* merge_scratch = static_cast<unsigned char*>(ws) + keys_bytes(g) + nvalid_bytes(g);
   const int istride = key_stride(g);
 
-  const int fparts = forward_parts();
+  const int fparts = opt.forward_parts;
   // Outputs per lane: more of them amortise the per-step cost (list entry, address, vote) over more
   // outputs, fewer give more (row, output block) items to spread over the SMs. `cost` is the measured number
   // of instructions per warp-step, `ctas` how many CTAs fit per SM; with few items pick the smallest
   // estimate of (waves of items) x (cost of a step).
-  auto pick = [&](int unit, const double (&cost)[3], const int (&ctas)[3], int top) {
+  auto pick = [&](int unit, const double (&cost)[4], const int (&ctas)[4], int top) {
     int best_c = top;
     const double items_top = (double)g.R * ((g.J + unit * (1 << top) - 1) / (unit * (1 << top)));
     if (items_top < 4.0 * li.num_sms * ctas[top] * kFwdWarps) {
@@ -959,20 +997,22 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     return best_c;
   };
   // Variants of the walk: 1 = output pairs in 64-bit registers, 64 outputs per warp (fan-out <= 64, or few rows:
-  // more warps); 3 = scalar, 2 or 4 consecutive outputs per lane read by one 8/16-byte load (fan-out > 64);
+  // more warps); 3 = scalar, 2, 4 or 8 consecutive outputs per lane read by 8/16-byte loads (fan-out > 64);
   // 2 = scalar with outputs lane + 32*m (odd fan-out or unaligned weights).
   const bool al8 = (g.J % 2 == 0) && (reinterpret_cast<uintptr_t>(w) % 8 == 0);
   const bool al16 = (g.J % 4 == 0) && (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  const double cost[3] = {19.0, 24.0, 39.0};
-  const int ctas[3] = {6, 4, 4};
-  int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
+  const bool al32 = al16 && (g.J % 8 == 0);
+  const double cost[4] = {19.0, 24.0, 39.0, 62.0};
+  const int ctas[4] = {6, 4, 4, 2};
+  int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : (g.J <= 128 ? 2 : 3)));
   int variant = 2;
   if (al8) variant = (g.J <= 64 || jsel < 2) ? 1 : 3;
-  if (((fparts >> 4) & 3) != 0) {   // measurement aid
-    variant = (fparts >> 4) & 3;
+  if (opt.walk_layout != 0) {
+    variant = opt.walk_layout;
     if (variant != 2 && !al8) variant = 2;
   }
-  if (((fparts >> 2) & 3) != 0) jsel = ((fparts >> 2) & 3) - 1;   // measurement aid: force the outputs per lane
+  if (opt.walk_outputs != 0) jsel = opt.walk_outputs - 1;
+  if (jsel == 3 && !(variant == 3 && al32)) jsel = 2;   // eight outputs per lane exist only as consecutive outputs
   if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
@@ -980,11 +1020,20 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     if (variant == 3) {
       if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-      return launch_walk<4, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      if (jsel == 2) return launch_walk<4, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      return launch_walk<8, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     }
     if (jsel == 1) return launch_walk<2, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
     return launch_walk<4, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
   };
+
+  if (use_merge_lists(g, opt)) {
+    if (fparts & 1) {
+      const int rc = launch_merge_lists(g, x, keys_g, nvalid_g, istride, merge_scratch, li, s);
+      if (rc != OK) return rc;
+    }
+    return walk(s, 0, g.R);
+  }
 
   const size_t budget = (size_t)li.max_smem_optin - 1024;
   const size_t per_warp = sort_bytes_per_warp(g.I);
@@ -996,9 +1045,11 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
     if (cudaFuncSetAttribute(snn_sort_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget) != cudaSuccess)
       return E_CUDA;
     int grid = g.R < li.num_sms ? g.R : li.num_sms;
-    snn_sort_long_kernel<<<grid, kFwdThreads, smem, s>>>(g, x, keys_g, nvalid_g, istride);
-    count_launch();
-    if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+    if (fparts & 1) {
+      snn_sort_long_kernel<<<grid, kFwdThreads, smem, s>>>(g, x, keys_g, nvalid_g, istride);
+      count_launch();
+      if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+    }
     return walk(s, 0, g.R);
   }
 

@@ -1,0 +1,231 @@
+// Sorted input lists of a stride-1 convolution (SnnCv, snntc/snncv_kernels.cu.cc:111-167: the reference
+// materialises every receptive field with extract_image_patches and sorts each one with a segmented sort).
+//
+// Neighbouring receptive fields of a 3x3 stride-1 convolution share six of their nine input pixels, so sorting
+// every field on its own sorts every input value nine times. Here every input value is sorted ONCE and the
+// fields are assembled by merging:
+//   1. pixel runs   one warp per input pixel: the pixel's C channel values, minus those that never spike
+//                   (> MAX - 0.1, NaN), sorted by a bitonic network held in registers (shuffles between lanes);
+//   2. row runs     one thread per (input row h, output column nw): sequential merge of the Kw pixel runs
+//                   (h, nw - pad_left + kw) -- shared by the Kh receptive fields that contain that row segment;
+//   3. field lists  one thread per receptive field: sequential merge of its Kh row runs, written in the format
+//                   the walk kernels read: (x, element offset of weight row ((kh*Kw+kw)*C+c)).
+// A sequential two- or three-way merge costs a few dozen instructions per entry and thread and needs no
+// cooperation between threads; the per-field radix sort it replaces spends about five hundred per entry.
+// The order among equal input values differs from a per-field sort's; no output can spike between two equal
+// inputs, so the walk's result does not depend on it.
+#include "snntc_common.cuh"
+#include "snntc_merge.cuh"
+
+#include <math_constants.h>
+
+namespace snntc {
+
+namespace {
+
+typedef unsigned long long u64;
+
+constexpr int kListThreads = 128;
+constexpr int kPixelWarps = 8;
+
+// Bitonic sort of 32*EPL keys, EPL per lane: element e = lane*EPL + m lives in v[m] of lane e / EPL.
+// Ascending; afterwards element e has rank e.
+template <int EPL>
+__device__ __forceinline__ void warp_bitonic_sort(u64 (&v)[EPL], int lane) {
+#pragma unroll
+  for (int k = 2; k <= 32 * EPL; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j >= 1; j >>= 1) {
+      if (j >= EPL) {
+        const int lj = j / EPL;                       // partner lane = lane ^ lj, same slot m
+        const bool lower = (lane & lj) == 0;          // this lane holds the lower index of each pair
+#pragma unroll
+        for (int m = 0; m < EPL; ++m) {
+          const u64 o = __shfl_xor_sync(0xffffffffu, v[m], lj);
+          const bool asc = (((lane * EPL + m) & k) == 0) || (k == 32 * EPL);
+          const bool take_min = (asc == lower);
+          const bool o_less = o < v[m];
+          v[m] = (take_min == o_less) ? o : v[m];
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < EPL; ++m) {
+          const int p = m ^ j;
+          if (p > m) {
+            const bool asc = (((lane * EPL + m) & k) == 0) || (k == 32 * EPL);
+            const u64 a = v[m], b = v[p];
+            const bool sw = asc ? (a > b) : (a < b);
+            v[m] = sw ? b : a;
+            v[p] = sw ? a : b;
+          }
+        }
+      }
+    }
+  }
+}
+
+// One warp per input pixel p = (b*H + h)*W + w: runs[p*stride ..] receives the pixel's inputs that can spike
+// as (float bits, c*J) in ascending order followed by a terminator; counts[p] their number.
+template <int EPL>
+__global__ void __launch_bounds__(kPixelWarps * 32)
+snn_pixel_runs_kernel(const float* __restrict__ x, int npix, int C, int J, float maxcomp,
+                      WalkEntry* __restrict__ runs, int* __restrict__ counts, int stride) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  for (int p = blockIdx.x * kPixelWarps + warp; p < npix; p += gridDim.x * kPixelWarps) {
+    const float* xp = x + (size_t)p * C;
+    u64 v[EPL];
+    int n = 0;
+#pragma unroll
+    for (int m = 0; m < EPL; ++m) {
+      const int c = m * 32 + lane;                    // coalesced: the network does not care where a key starts
+      float val = CUDART_INF_F;
+      if (c < C) val = __ldg(xp + c);
+      const bool keep = val <= maxcomp;               // false for NaN and for inputs that never spike
+      v[m] = keep ? (((u64)float_to_sortable(val) << 32) | (unsigned)c) : ~0ull;
+      n += __popc(__ballot_sync(0xffffffffu, keep));
+    }
+    warp_bitonic_sort<EPL>(v, lane);
+    WalkEntry* dst = runs + (size_t)p * stride;
+#pragma unroll
+    for (int m = 0; m < EPL; ++m) {
+      const int rank = lane * EPL + m;
+      if (rank < n)
+        dst[rank] = make_uint2(__float_as_uint(sortable_to_float((uint32_t)(v[m] >> 32))),
+                               (uint32_t)v[m] * (uint32_t)J);
+    }
+    if (lane == 0) {
+      dst[n] = make_uint2(kRunEndBits, 0u);
+      counts[p] = n;
+    }
+  }
+}
+
+__device__ const WalkEntry g_empty_run[2] = {{kRunEndBits, 0u}, {kRunEndBits, 0u}};
+
+// One thread per (b, h, nw): merge of the pixel runs (b, h, nw - pad_left + kw), kw < Kw, columns outside the
+// image being empty. Entry offsets gain kw*C*J.
+__global__ void __launch_bounds__(kListThreads)
+snn_row_runs_kernel(const Geometry g, const WalkEntry* __restrict__ pix, const int* __restrict__ pix_n, int pix_stride,
+                    WalkEntry* __restrict__ rows, int* __restrict__ rows_n, int row_stride) {
+  const int total_threads = g.B * g.H * g.Nw;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= total_threads) return;
+  const int nw = t % g.Nw;
+  const int bh = t / g.Nw;                            // b*H + h
+  const WalkEntry* run[3] = {g_empty_run, g_empty_run, g_empty_run};
+  uint32_t off[3] = {0u, 0u, 0u};
+  int total = 0;
+#pragma unroll
+  for (int kw = 0; kw < 3; ++kw) {
+    const int wc = nw - g.pad_left + kw;
+    if (kw < g.Kw && wc >= 0 && wc < g.W) {
+      const int p = bh * g.W + wc;
+      run[kw] = pix + (size_t)p * pix_stride;
+      total += __ldg(pix_n + p);
+    }
+    off[kw] = (uint32_t)kw * (uint32_t)g.C * (uint32_t)g.J;
+  }
+  merge3_runs<WalkEntry, uint4>(run[0], run[1], run[2], off[0], off[1], off[2], total,
+                                rows + (size_t)t * row_stride, true);
+  rows_n[t] = total;
+}
+
+// One thread per receptive field r = (b*Nh + nh)*Nw + nw: merge of the row runs (b, nh - pad_top + kh, nw),
+// kh < Kh, rows outside the image being empty. Entry offsets gain kh*Kw*C*J.
+__global__ void __launch_bounds__(kListThreads)
+snn_field_lists_kernel(const Geometry g, const WalkEntry* __restrict__ rows, const int* __restrict__ rows_n,
+                       int row_stride, WalkEntry* __restrict__ lists, int* __restrict__ nvalid, int istride) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= g.R) return;
+  const int nw = r % g.Nw;
+  const int t0 = r / g.Nw;
+  const int nh = t0 % g.Nh;
+  const int b = t0 / g.Nh;
+  const WalkEntry* run[3] = {g_empty_run, g_empty_run, g_empty_run};
+  uint32_t off[3] = {0u, 0u, 0u};
+  int total = 0;
+#pragma unroll
+  for (int kh = 0; kh < 3; ++kh) {
+    const int h = nh - g.pad_top + kh;
+    if (kh < g.Kh && h >= 0 && h < g.H) {
+      const int t = (b * g.H + h) * g.Nw + nw;
+      run[kh] = rows + (size_t)t * row_stride;
+      total += __ldg(rows_n + t);
+    }
+    off[kh] = (uint32_t)kh * (uint32_t)g.Kw * (uint32_t)g.C * (uint32_t)g.J;
+  }
+  merge3_runs<WalkEntry, uint4>(run[0], run[1], run[2], off[0], off[1], off[2], total,
+                                lists + (size_t)r * istride, false);
+  nvalid[r] = total;
+}
+
+int pixel_stride(const Geometry& g) { return (g.C + 2 + 1) & ~1; }            // entries per pixel run, even
+int row_stride(const Geometry& g) { return (g.Kw * g.C + 2 + 1) & ~1; }       // entries per row run, even
+size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+struct MergeScratch { size_t pix, pix_n, rows, rows_n, total; };
+MergeScratch merge_scratch(const Geometry& g) {
+  MergeScratch m;
+  const size_t npix = (size_t)g.B * g.H * g.W, nrow = (size_t)g.B * g.H * g.Nw;
+  m.pix = 0;
+  m.pix_n = m.pix + align256(npix * pixel_stride(g) * sizeof(WalkEntry));
+  m.rows = m.pix_n + align256(npix * sizeof(int));
+  m.rows_n = m.rows + align256(nrow * row_stride(g) * sizeof(WalkEntry));
+  m.total = m.rows_n + align256(nrow * sizeof(int));
+  return m;
+}
+
+}  // namespace
+
+bool merge_lists_supported(const Geometry& g) {
+  return merge_lists_shape_ok(g) && g.Sh == 1 && g.Sw == 1;
+}
+
+bool merge_lists_shape_ok(const Geometry& g) {
+  if (!g.is_conv) return false;
+  if (g.Kh < 1 || g.Kh > 3 || g.Kw < 1 || g.Kw > 3 || g.Kh * g.Kw < 2) return false;
+  if (g.C < 16 || g.C > 512) return false;            // fewer channels: the per-pixel warps would idle; more: registers
+  // every intermediate index stays inside 32 bits
+  if ((long long)g.B * g.H * g.W * pixel_stride(g) > 0x7fffffffLL) return false;
+  if ((long long)g.B * g.H * g.Nw * row_stride(g) > 0x7fffffffLL) return false;
+  return true;
+}
+
+size_t merge_lists_bytes(const Geometry& g) { return merge_scratch(g).total; }
+
+int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
+                       void* scratch, const LaunchInfo& li, cudaStream_t s) {
+  const MergeScratch m = merge_scratch(g);
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  WalkEntry* pix = reinterpret_cast<WalkEntry*>(base + m.pix);
+  int* pix_n = reinterpret_cast<int*>(base + m.pix_n);
+  WalkEntry* rows = reinterpret_cast<WalkEntry*>(base + m.rows);
+  int* rows_n = reinterpret_cast<int*>(base + m.rows_n);
+  const int npix = g.B * g.H * g.W;
+  const int ps = pixel_stride(g), rs = row_stride(g);
+  const float maxcomp = g.maxv - 0.1f;
+
+  long grid = ((long)npix + kPixelWarps - 1) / kPixelWarps;
+  const long cap = (long)li.num_sms * 8;
+  if (grid > cap) grid = cap;
+  const int epl = (g.C + 31) / 32;
+  if (epl <= 1) snn_pixel_runs_kernel<1><<<(int)grid, kPixelWarps * 32, 0, s>>>(x, npix, g.C, g.J, maxcomp, pix, pix_n, ps);
+  else if (epl <= 2) snn_pixel_runs_kernel<2><<<(int)grid, kPixelWarps * 32, 0, s>>>(x, npix, g.C, g.J, maxcomp, pix, pix_n, ps);
+  else if (epl <= 4) snn_pixel_runs_kernel<4><<<(int)grid, kPixelWarps * 32, 0, s>>>(x, npix, g.C, g.J, maxcomp, pix, pix_n, ps);
+  else if (epl <= 8) snn_pixel_runs_kernel<8><<<(int)grid, kPixelWarps * 32, 0, s>>>(x, npix, g.C, g.J, maxcomp, pix, pix_n, ps);
+  else snn_pixel_runs_kernel<16><<<(int)grid, kPixelWarps * 32, 0, s>>>(x, npix, g.C, g.J, maxcomp, pix, pix_n, ps);
+  count_launch();
+  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+
+  const int nrow = g.B * g.H * g.Nw;
+  snn_row_runs_kernel<<<(nrow + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, pix, pix_n, ps, rows, rows_n, rs);
+  count_launch();
+  if (cudaGetLastError() != cudaSuccess) return E_CUDA;
+
+  snn_field_lists_kernel<<<(g.R + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
+}
+
+}  // namespace snntc

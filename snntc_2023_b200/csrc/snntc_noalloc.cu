@@ -4,8 +4,10 @@
 // a plugin called from inside another framework's executor that hands out only the operator's
 // declared inputs and outputs, a real-time loop that fixed its memory plan up front, or a process
 // whose device memory is owned by someone else's pool. The regular entry point needs a caller-owned
-// workspace for the partial weight-gradient tiles; this variant keeps that workspace inside the
-// library image instead, as one fixed array in device global memory.
+// workspace (u = grad/(sum w - theta) for every output, the range flag of the weight-gradient kernel
+// and its partial tiles); this variant keeps that workspace inside the library image instead, as one
+// fixed array in device global memory. It runs its kernels on the caller's stream only -- the
+// auxiliary streams of the regular entry point are created on first use, which is an allocation.
 #include "../../include/snntc_b200.h"
 #include "snntc_common.cuh"
 
@@ -32,17 +34,18 @@ bool g_ready[kMaxDevices];
 // launch planning needs. Runs with that device current. Nothing here allocates.
 int setup_current_device(int* dev_out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return SNNTC_E_CUDA;
+  cudaError_t e0 = cudaGetDevice(&dev);
+  if (e0 != cudaSuccess) { snntc::note_cuda_error(e0); return SNNTC_E_CUDA; }
   if (dev < 0 || dev >= kMaxDevices) return SNNTC_E_UNSUPPORTED;
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_ready[dev]) {
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess || ptr == nullptr) return SNNTC_E_CUDA;
+    if (e != cudaSuccess || ptr == nullptr) { snntc::note_cuda_error(e); return SNNTC_E_CUDA; }
     int sms = 0, smem = 0;
     e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
-    if (e != cudaSuccess) return SNNTC_E_CUDA;
+    if (e != cudaSuccess) { snntc::note_cuda_error(e); return SNNTC_E_CUDA; }
     g_scratch_addr[dev] = ptr;
     g_launch_info[dev].num_sms = sms;
     g_launch_info[dev].max_smem_optin = smem;
@@ -81,11 +84,18 @@ int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, const float
   const size_t need = snntc::backward_workspace_bytes(g, li);
   if (need > kScratchBytes) return SNNTC_E_WORKSPACE;
 
-  if (dparams6 && cudaMemsetAsync(dparams6, 0, 6 * sizeof(float), (cudaStream_t)stream) != cudaSuccess) return SNNTC_E_CUDA;
-  // Nothing in the scratch has to start at zero: the weight-gradient kernel writes every partial tile
-  // the reduction reads, so whatever the previous call left there is overwritten first.
-  return snntc::launch_backward(g, grad_2BJ, x, w, out_2BJ, dx, dw, g_scratch_addr[dev], kScratchBytes, li,
-                                (cudaStream_t)stream);
+  if (dparams6) {
+    const cudaError_t e = cudaMemsetAsync(dparams6, 0, 6 * sizeof(float), (cudaStream_t)stream);
+    if (e != cudaSuccess) { snntc::note_cuda_error(e); return SNNTC_E_CUDA; }
+  }
+  // Nothing in the scratch has to start at zero: u, the flag and every partial tile the reduction reads are
+  // written by this call's own kernels before they are read, whatever the previous call left there.
+  snntc::Options opt;
+  opt.overlap = 0;   // one stream: no auxiliary stream or event is ever created on behalf of this entry point
+  rc = snntc::launch_backward(g, grad_2BJ, x, w, out_2BJ, dx, dw, g_scratch_addr[dev], kScratchBytes, li, opt,
+                              (cudaStream_t)stream);
+  if (rc == snntc::E_CUDA) snntc::note_cuda_error(cudaGetLastError());
+  return rc;
 }
 
 }  // extern "C"

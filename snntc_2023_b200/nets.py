@@ -70,7 +70,13 @@ def layer_work(specs, in_shape):
 class SnnNet(torch.nn.Module):
     """The layers of `specs` in order. All weights live in one flat fp32 buffer (`flat_param`) and
     all weight gradients are written by the backward kernels straight into a second flat buffer
-    (`flat_grad`), which is what a data-parallel step all-reduces and the optimiser consumes."""
+    (`flat_grad`), which is what a data-parallel step all-reduces and the optimiser consumes.
+
+    The operators WRITE their dW into flat_grad (they do not accumulate), and autograd is told nothing
+    about it. Any other term of the objective that depends on the weights (the reference's
+    constraint_cost, snntc-mnist.py:55-59) reaches a weight through autograd's own `.grad`; `backward`
+    below runs autograd and then folds those `.grad` tensors into flat_grad, so that flat_grad holds
+    the gradient of the whole objective whatever the order in which autograd visited the terms."""
 
     def __init__(self, specs, weights=None, biasvolt=1.0, device="cuda"):
         super().__init__()
@@ -109,7 +115,6 @@ class SnnNet(torch.nn.Module):
             self.flat_param[off:off + n].copy_(l.weight.data.reshape(-1))
             l.weight.data = self.flat_param[off:off + n].view_as(l.weight)
             l.grad_sink = self.flat_grad[off:off + n].view_as(l.weight)
-            l.weight.grad = l.grad_sink
             off += n
 
     def forward(self, x):
@@ -119,3 +124,22 @@ class SnnNet(torch.nn.Module):
 
     def loss(self, x, labels):
         return loss_func(self.forward(x), labels)
+
+    def constraint_cost(self, K, K2):
+        """K * sum_layers mean_j max(0, 1 - sum_i w_ij) + K2 * sum_layers mean(w^2) over this network's weights
+        (MyModel.constraint_cost of the reference's trainers, snntc-mnist.py:55-59); differentiable."""
+        from . import train
+        return train.constraint_cost([l.weight for l in self.weighted_layers()], K, K2)
+
+    def backward(self, objective):
+        """objective.backward(), after which flat_grad holds d objective / d weights: the operators' dW (written
+        by the kernels) plus whatever autograd accumulated in a weight's .grad for the other terms. The .grad
+        of every weight is left pointing at its slice of flat_grad, for optimisers that read .grad."""
+        ws = self.weighted_layers()
+        for l in ws:
+            l.weight.grad = None
+        objective.backward()
+        for l in ws:
+            if l.weight.grad is not None:
+                l.grad_sink.add_(l.weight.grad)
+            l.weight.grad = l.grad_sink

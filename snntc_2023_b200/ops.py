@@ -22,29 +22,11 @@ import torch
 from . import _lib
 
 
-# ------------------------------------------------------------------------------------------ profiling hook
-class Profile:
-    """When `Profile.records` is a list, every library call appends (tag, dims, start_event, end_event)
-    recorded on the calling stream; used by bench.py to time the kernels of a step one by one."""
-    records = None
-    split_forward = False   # also time each forward call's sort kernel alone (tag "<op>_forward_sort")
-    forward_bits = 0        # extra bits for snntc_profile_forward_parts while split_forward toggles it
-
-    @staticmethod
-    def begin(t):
-        if Profile.records is None:
-            return None
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record(torch.cuda.current_stream(t.device))
-        return ev
-
-    @staticmethod
-    def end(ev, t, tag, dims):
-        if ev is None:
-            return
-        ev1 = torch.cuda.Event(enable_timing=True)
-        ev1.record(torch.cuda.current_stream(t.device))
-        Profile.records.append((tag, dims, ev, ev1))
+# ------------------------------------------------------------------------------------------ replay tap
+# When TAP is a list, the layer forms below append what their backward was called with:
+# (kind, x, weight, params, geom, packed forward output, upstream gradient). bench.py sets it for one step and
+# then times the kernels of every layer apart on exactly those tensors; nothing else reads it.
+TAP = None
 
 
 # ------------------------------------------------------------------------------------------ helpers
@@ -85,6 +67,11 @@ def _ptr(t):
     return 0 if t is None else t.data_ptr()
 
 
+def _opts_ptr(opts):
+    import ctypes
+    return ctypes.cast(opts, ctypes.c_void_p).value
+
+
 def conv_geometry(H, W, Kh, Kw, Sh, Sw, padding):
     """(pad_top, pad_left, Nh, Nw) of SNN_conv: SAME pads with MAX by
     total=(ceil(H/S)-1)*S+K-H, before=total//2; VALID drops trailing rows/columns
@@ -102,51 +89,57 @@ def conv_geometry(H, W, Kh, Kw, Sh, Sw, padding):
 
 
 # ------------------------------------------------------------------------------------------ raw ops
-def snn_fc(inp, weight, params):
-    lib = _lib.load()
+# `opts` (an opts7 vector from _lib.options) selects kernels explicitly through the measurement build of the
+# library; `workspace` lets a caller keep the scratch between two calls (lists built by one, walked by the next).
+def snn_fc(inp, weight, params, opts=None, workspace=None, out=None):
     x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 6)
     if x.dim() != 2 or w.dim() != 2:
         raise ValueError("snn_fc expects in[B,I] and weight[rows,J]")
     B, I = x.shape
     rows, J = w.shape
+    lib = _lib.load() if opts is None else _lib.load_measure()
     with torch.cuda.device(x.device):
-        out = torch.empty((2 * B, J), dtype=torch.float32, device=x.device)
-        ws, wsb = _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
-        if Profile.records is not None and Profile.split_forward:
-            lib.snntc_profile_forward_parts(1 | Profile.forward_bits)
-            ev = Profile.begin(x)
-            lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
-                                 _ptr(ws), wsb, _stream(x))
-            Profile.end(ev, x, "fc_forward_sort", (B, rows, J))
-            lib.snntc_profile_forward_parts(3 | Profile.forward_bits)
-        ev = Profile.begin(x)
-        rc = lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
-                                  _ptr(ws), wsb, _stream(x))
-        Profile.end(ev, x, "fc_forward", (B, rows, J))
+        if out is None:
+            out = torch.empty((2 * B, J), dtype=torch.float32, device=x.device)
+        ws, wsb = (workspace, workspace.numel() * 4) if workspace is not None else \
+            _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
+        if opts is None:
+            rc = lib.snntc_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
+                                      _ptr(ws), wsb, _stream(x))
+        else:
+            rc = lib.snntc_measure_fc_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
+                                              _ptr(ws), wsb, _opts_ptr(opts), _stream(x))
     _lib.check(rc, "SnnFc")
     return out
 
 
-def snn_fc_infer(inp, weight, params):
-    """Spike values only, [B,J]: SnnFc without the 1/(sum w - theta) half (snntc_fc_infer)."""
+def fc_forward_workspace(B, I, J, device):
+    lib = _lib.load()
+    return _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), device)[0]
+
+
+def snn_fc_infer(inp, weight, params, khist=None):
+    """Spike values only, [B,J]: SnnFc without the 1/(sum w - theta) half (snntc_fc_infer). `khist`: an int32
+    CUDA tensor of I+2 zeros (I without the bias row) that receives the histogram of causal-set sizes."""
     lib = _lib.load()
     x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 6)
     if x.dim() != 2 or w.dim() != 2:
         raise ValueError("snn_fc_infer expects in[B,I] and weight[rows,J]")
     B, I = x.shape
     rows, J = w.shape
+    if khist is not None and (khist.dtype != torch.int32 or khist.numel() < I + 2 or not khist.is_cuda):
+        raise ValueError("khist must be an int32 CUDA tensor of at least fan_in + 2 elements")
     with torch.cuda.device(x.device):
         out = torch.empty((B, J), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_fc_forward_workspace_bytes(B, I, J), x.device)
-        rc = lib.snntc_fc_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, I, rows, J,
+        rc = lib.snntc_fc_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), _ptr(khist), B, I, rows, J,
                                 _ptr(ws), wsb, _stream(x))
     _lib.check(rc, "SnnFc (inference)")
     return out
 
 
-def snn_fc_grad(grad, inp, weight, params, oldout, need_input_grad=True, grad_weight_out=None):
+def snn_fc_grad(grad, inp, weight, params, oldout, need_input_grad=True, grad_weight_out=None, opts=None):
     """grad may be the packed [2B,J] tensor or just its first B rows (only those are read)."""
-    lib = _lib.load()
     g = _as_cuda_f32(grad, "grad"); x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight")
     y = _as_cuda_f32(oldout, "oldout"); p = _params(params, 6)
     B, I = x.shape
@@ -155,15 +148,19 @@ def snn_fc_grad(grad, inp, weight, params, oldout, need_input_grad=True, grad_we
         raise ValueError("snn_fc_grad: oldout must be [2B,J]")
     if g.shape[0] not in (B, 2 * B) or g.shape[1] != J:
         raise ValueError("snn_fc_grad: Grad/Oldout batch should be 2 * batch")
+    lib = _lib.load() if opts is None else _lib.load_measure()
     with torch.cuda.device(x.device):
         dx = torch.empty_like(x) if need_input_grad else None
         dw = grad_weight_out if grad_weight_out is not None else torch.empty_like(w)
         dp = torch.empty(6, dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_fc_backward_workspace_bytes(B, I, rows, J), x.device)
-        ev = Profile.begin(x)
-        rc = lib.snntc_fc_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
-                                   _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, I, rows, J, _ptr(ws), wsb, _stream(x))
-        Profile.end(ev, x, "fc_backward", (B, rows, J, need_input_grad))
+        if opts is None:
+            rc = lib.snntc_fc_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
+                                       _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, I, rows, J, _ptr(ws), wsb, _stream(x))
+        else:
+            rc = lib.snntc_measure_fc_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
+                                               _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, I, rows, J, _ptr(ws), wsb,
+                                               _opts_ptr(opts), _stream(x))
     _lib.check(rc, "SnnFcGrad")
     return dx, dw, dp
 
@@ -181,51 +178,58 @@ def _cv_dims(x, w, p, pad_top, pad_left, Nh, Nw):
     return B, H, W, C, rows, Kc, Kh, Kw, pad_top, pad_left, Nh, Nw
 
 
-def snn_cv(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
+def snn_cv(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None, opts=None, workspace=None, out=None):
     """With the default pad arguments this is the reference op: `inp` is the tensor SNN_conv.call has
     already padded with MAX (SAME) or cropped (VALID)."""
-    lib = _lib.load()
     x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 12)
     B, H, W, C, rows, Kc, Kh, Kw, pt, pl, Nh, Nw = _cv_dims(x, w, p, pad_top, pad_left, Nh, Nw)
     if Nh <= 0 or Nw <= 0:
         raise ValueError("snn_cv: kernel larger than the (padded) input")
+    lib = _lib.load() if opts is None else _lib.load_measure()
     with torch.cuda.device(x.device):
-        out = torch.empty((2 * B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
-        ws, wsb = _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
-        if Profile.records is not None and Profile.split_forward:
-            lib.snntc_profile_forward_parts(1 | Profile.forward_bits)
-            ev = Profile.begin(x)
-            lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
-                                 pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
-            Profile.end(ev, x, "cv_forward_sort", (B * Nh * Nw, rows, Kc))
-            lib.snntc_profile_forward_parts(3 | Profile.forward_bits)
-        ev = Profile.begin(x)
-        rc = lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
-                                  pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
-        Profile.end(ev, x, "cv_forward", (B * Nh * Nw, rows, Kc))
+        if out is None:
+            out = torch.empty((2 * B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
+        ws, wsb = (workspace, workspace.numel() * 4) if workspace is not None else \
+            _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
+        if opts is None:
+            rc = lib.snntc_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
+                                      pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
+        else:
+            rc = lib.snntc_measure_cv_forward(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C,
+                                              rows, Kc, pt, pl, Nh, Nw, _ptr(ws), wsb, _opts_ptr(opts), _stream(x))
     _lib.check(rc, "SnnCv")
     return out
 
 
-def snn_cv_infer(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None):
-    """Spike values only, [B,Nh,Nw,Kc]: SnnCv without the 1/(sum w - theta) half (snntc_cv_infer)."""
+def cv_forward_workspace(x, weight, params, Nh, Nw):
+    lib = _lib.load()
+    p = _params(params, 12)
+    B, H, W, C = x.shape
+    return _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, weight.shape[1], int(p[6]), int(p[7]), Nh, Nw),
+                      x.device)[0]
+
+
+def snn_cv_infer(inp, weight, params, pad_top=0, pad_left=0, Nh=None, Nw=None, khist=None):
+    """Spike values only, [B,Nh,Nw,Kc]: SnnCv without the 1/(sum w - theta) half (snntc_cv_infer). `khist`: an
+    int32 CUDA tensor of Kh*Kw*C+2 zeros that receives the histogram of causal-set sizes."""
     lib = _lib.load()
     x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 12)
     B, H, W, C, rows, Kc, Kh, Kw, pt, pl, Nh, Nw = _cv_dims(x, w, p, pad_top, pad_left, Nh, Nw)
     if Nh <= 0 or Nw <= 0:
         raise ValueError("snn_cv_infer: kernel larger than the (padded) input")
+    if khist is not None and (khist.dtype != torch.int32 or khist.numel() < Kh * Kw * C + 2 or not khist.is_cuda):
+        raise ValueError("khist must be an int32 CUDA tensor of at least fan_in + 2 elements")
     with torch.cuda.device(x.device):
         out = torch.empty((B, Nh, Nw, Kc), dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_cv_forward_workspace_bytes(B, H, W, C, Kc, Kh, Kw, Nh, Nw), x.device)
-        rc = lib.snntc_cv_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), B, H, W, C, rows, Kc,
-                                pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
+        rc = lib.snntc_cv_infer(x.data_ptr(), w.data_ptr(), p.ctypes.data, out.data_ptr(), _ptr(khist), B, H, W, C,
+                                rows, Kc, pt, pl, Nh, Nw, _ptr(ws), wsb, _stream(x))
     _lib.check(rc, "SnnCv (inference)")
     return out
 
 
 def snn_cv_grad(grad, inp, weight, params, oldout, pad_top=0, pad_left=0, need_input_grad=True,
-                grad_weight_out=None):
-    lib = _lib.load()
+                grad_weight_out=None, opts=None):
     g = _as_cuda_f32(grad, "grad"); x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight")
     y = _as_cuda_f32(oldout, "oldout"); p = _params(params, 12)
     if y.dim() != 4:
@@ -235,16 +239,20 @@ def snn_cv_grad(grad, inp, weight, params, oldout, pad_top=0, pad_left=0, need_i
         raise ValueError("snn_cv_grad: oldout must be [2B,Nh,Nw,Kc]")
     if g.shape[0] not in (B, 2 * B) or tuple(g.shape[1:]) != tuple(y.shape[1:]):
         raise ValueError("snn_cv_grad: Grad/Oldout batch should be 2 * batch")
+    lib = _lib.load() if opts is None else _lib.load_measure()
     with torch.cuda.device(x.device):
         dx = torch.empty_like(x) if need_input_grad else None
         dw = grad_weight_out if grad_weight_out is not None else torch.empty_like(w)
         dp = torch.empty(12, dtype=torch.float32, device=x.device)
         ws, wsb = _workspace(lib.snntc_cv_backward_workspace_bytes(B, H, W, C, rows, Kc, Nh, Nw), x.device)
-        ev = Profile.begin(x)
-        rc = lib.snntc_cv_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
-                                   _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, H, W, C, rows, Kc, pt, pl, Nh, Nw,
-                                   _ptr(ws), wsb, _stream(x))
-        Profile.end(ev, x, "cv_backward", (B * Nh * Nw, rows, Kc, need_input_grad))
+        if opts is None:
+            rc = lib.snntc_cv_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
+                                       _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, H, W, C, rows, Kc, pt, pl, Nh, Nw,
+                                       _ptr(ws), wsb, _stream(x))
+        else:
+            rc = lib.snntc_measure_cv_backward(g.data_ptr(), x.data_ptr(), w.data_ptr(), p.ctypes.data, y.data_ptr(),
+                                               _ptr(dx), dw.data_ptr(), dp.data_ptr(), B, H, W, C, rows, Kc, pt, pl,
+                                               Nh, Nw, _ptr(ws), wsb, _opts_ptr(opts), _stream(x))
     _lib.check(rc, "SnnCvGrad")
     return dx, dw, dp
 
@@ -311,7 +319,10 @@ class _SnnFcLayer(torch.autograd.Function):
     def backward(ctx, grad):
         X, W, out = ctx.saved_tensors
         need_dx = ctx.needs_input_grad[0]
-        dx, dw, _ = snn_fc_grad(grad.contiguous(), X, W, ctx.params, out, need_input_grad=need_dx,
+        grad = grad.contiguous()
+        if TAP is not None:
+            TAP.append(("fc", X, W, ctx.params, None, out, grad, need_dx))
+        dx, dw, _ = snn_fc_grad(grad, X, W, ctx.params, out, need_input_grad=need_dx,
                                 grad_weight_out=ctx.sink)
         return dx, (None if ctx.sink is not None else dw), None, None
 
@@ -332,7 +343,10 @@ class _SnnCvLayer(torch.autograd.Function):
         X, W, out = ctx.saved_tensors
         pt, pl, _, _ = ctx.geom
         need_dx = ctx.needs_input_grad[0]
-        dx, dw, _ = snn_cv_grad(grad.contiguous(), X, W, ctx.params, out, pt, pl, need_input_grad=need_dx,
+        grad = grad.contiguous()
+        if TAP is not None:
+            TAP.append(("cv", X, W, ctx.params, ctx.geom, out, grad, need_dx))
+        dx, dw, _ = snn_cv_grad(grad, X, W, ctx.params, out, pt, pl, need_input_grad=need_dx,
                                 grad_weight_out=ctx.sink)
         return dx, (None if ctx.sink is not None else dw), None, None, None
 
@@ -342,13 +356,13 @@ def _no_grad_needed(X, W):
 
 
 def snn_fc_layer(X, W, params, grad_sink=None):
-    if _no_grad_needed(X, W) and Profile.records is None:   # evaluation: nothing will read 1/(sum w - theta)
+    if _no_grad_needed(X, W):   # evaluation: nothing will read 1/(sum w - theta)
         return snn_fc_infer(X, W, params)
     return _SnnFcLayer.apply(X, W, params, grad_sink)
 
 
 def snn_cv_layer(X, W, params, geom, grad_sink=None):
-    if _no_grad_needed(X, W) and Profile.records is None:
+    if _no_grad_needed(X, W):
         pt, pl, Nh, Nw = geom
         return snn_cv_infer(X, W, params, pt, pl, Nh, Nw)
     return _SnnCvLayer.apply(X, W, params, geom, grad_sink)
@@ -374,6 +388,7 @@ class _MinPool(torch.autograd.Function):
         _lib.check(rc, "minpool forward")
         ctx.save_for_backward(arg)
         ctx.in_shape = tuple(x.shape)
+        ctx.window = (Kh, Kw, Sh, Sw, pt, pl, Nh, Nw)
         return y
 
     @staticmethod
@@ -383,7 +398,8 @@ class _MinPool(torch.autograd.Function):
         gy = gy.contiguous()
         with torch.cuda.device(gy.device):
             dx = torch.empty(ctx.in_shape, dtype=torch.float32, device=gy.device)
-            rc = lib.snntc_minpool_backward(gy.data_ptr(), arg.data_ptr(), dx.data_ptr(), gy.numel(), dx.numel(),
+            B, H, W, C = ctx.in_shape
+            rc = lib.snntc_minpool_backward(gy.data_ptr(), arg.data_ptr(), dx.data_ptr(), B, H, W, C, *ctx.window,
                                             _stream(gy))
         _lib.check(rc, "minpool backward")
         return dx, None, None, None, None, None, None

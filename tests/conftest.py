@@ -30,3 +30,16 @@ def pytest_collection_modifyitems(config, items):
 def _built_oracle():
     from oracle import build
     build.build_oracle()
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """How much of every forward tensor was held to which bound (oracle/parity.py) goes to a report beside the
+    other outputs of a GPU run and, in short, to the terminal."""
+    from oracle import parity
+    if not parity.REPORT:
+        return
+    try:
+        parity.dump_report(os.path.join(ROOT, "gpurun_out", "parity_report.json"))
+    except OSError:
+        pass
+    print("\nparity summary: %s" % (parity.summary(),))

@@ -13,20 +13,45 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _declared_symbols():
+    """(symbols of the product library, symbols of the measurement build only) as the header declares them."""
     text = open(os.path.join(ROOT, "include", "snntc_b200.h")).read()
-    return sorted(set(re.findall(r"SNNTC_API[^;(]*?\b(snntc_\w+)\s*\(", text)))
+    head, _, rest = text.partition("#ifdef SNNTC_MEASURE")
+    measure, _, tail = rest.partition("#endif /* SNNTC_MEASURE */")
+    find = lambda t: sorted(set(re.findall(r"SNNTC_API[^;(]*?\b(snntc_\w+)\s*\(", t)))
+    return find(head + tail), find(measure)
+
+
+def _exported(path):
+    import subprocess
+    out = subprocess.check_output(["nm", "-D", "--defined-only", path], text=True)
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
 
 
 def test_library_exports_every_declared_symbol():
     from snntc_2023_b200 import _lib
     lib = _lib.load()
-    names = _declared_symbols()
-    assert len(names) >= 17
+    names, measure_names = _declared_symbols()
+    assert len(names) >= 24 and len(measure_names) == 5
     for n in names:
         assert hasattr(lib, n), "libsnntc_b200.so does not export %s" % n
     assert set(names) == set(_lib.SYMBOLS), "ctypes table and header disagree: %s" % (set(names) ^ set(_lib.SYMBOLS))
+    assert set(measure_names) == set(_lib.MEASURE_SYMBOLS)
     assert lib.snntc_version().startswith(b"snntc_b200")
     assert lib.snntc_status_string(0) == b"ok"
+
+
+def test_default_library_has_no_measurement_entry_points():
+    """Kernel selection and partial execution exist only in the measurement build: the product library exports
+    exactly what the header declares outside SNNTC_MEASURE, and no switch that changes what a call launches."""
+    from snntc_2023_b200 import _lib
+    names, measure_names = _declared_symbols()
+    exported = {s for s in _exported(_lib.LIB_PATH) if s.startswith("snntc_")}
+    assert exported == set(names), "unexpected exports: %s" % sorted(exported ^ set(names))
+    assert not any("profile" in s or "measure" in s or "probe" in s for s in exported)
+    m = _lib.load_measure()
+    for n in names + measure_names:
+        assert hasattr(m, n), "libsnntc_b200_measure.so does not export %s" % n
+    assert b"measurement" in m.snntc_version()
 
 
 def test_validation_status_codes_without_a_device():
@@ -54,6 +79,10 @@ def test_validation_status_codes_without_a_device():
         assert len(lib.snntc_status_string(code)) > 1
     assert lib.snntc_fc_forward_workspace_bytes(256, 784, 400) >= 256 * 784 * 8
     assert lib.snntc_fc_backward_workspace_bytes(1, 25088, 25089, 1024) == 4096 + 256   # u[1,1024] and the range flag: enough tiles, no row split
+    # a 3x3 stride-1 convolution also gets the scratch of the merging list builder; a 5x5 one does not
+    lists = 2 * 8 * 8 * 290 * 8
+    assert lib.snntc_cv_forward_workspace_bytes(2, 8, 8, 32, 16, 3, 3, 8, 8) > lists + 2 * 8 * 8 * 34 * 8
+    assert lib.snntc_cv_forward_workspace_bytes(2, 8, 8, 32, 16, 5, 5, 8, 8) < 2 * 8 * 8 * 802 * 8 + 4096
 
 
 def test_no_cpu_fallback():
@@ -127,3 +156,53 @@ def test_network_specs_and_work_counts():
     assert [w.shape for w in ws] == [(785, 400), (401, 400), (401, 10)] and all(not w[-1].any() for w in ws)
     ws2 = nets.spec_weights(nets.MNIST_MLP, 5)
     assert all(np.array_equal(a, b) for a, b in zip(ws, ws2))                 # same seed, same bytes on every rank
+
+
+def test_sequential_merge_of_sorted_runs_on_the_host():
+    """The three-way merge the list-building kernels run per thread (csrc/snntc_merge.cuh) is plain C++: compiled
+    for the host here and checked against numpy on random runs, empty runs and ties."""
+    import subprocess
+    import tempfile
+    src = r"""
+#include <stdint.h>
+#include <string.h>
+struct uint2 { unsigned x, y; };
+struct uint4 { unsigned x, y, z, w; };
+#include "%s"
+extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned oa, unsigned ob, unsigned oc,
+                       int total, uint2* dst, int terminate) {
+  snntc::merge3_runs<uint2, uint4>(a, b, c, oa, ob, oc, total, dst, terminate != 0);
+}
+""" % os.path.join(ROOT, "snntc_2023_b200", "csrc", "snntc_merge.cuh")
+    with tempfile.TemporaryDirectory() as d:
+        cpp = os.path.join(d, "m.cpp"); so = os.path.join(d, "m.so")
+        open(cpp, "w").write(src)
+        subprocess.check_call(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", so, cpp])
+        lib = ctypes.CDLL(so)
+        rng = np.random.default_rng(0)
+        for trial in range(200):
+            n = [int(rng.integers(0, 40)) if rng.random() > 0.2 else 0 for _ in range(3)]
+            runs, offs = [], [int(rng.integers(0, 1000)) for _ in range(3)]
+            for k in range(3):
+                vals = np.sort(np.round(np.exp(rng.random(n[k]) * 2), 1 if trial % 2 else 6).astype(np.float32))   # odd trials: many ties
+                ent = np.zeros((n[k] + 1, 2), np.uint32)
+                ent[:n[k], 0] = vals.view(np.uint32)
+                ent[:n[k], 1] = rng.integers(0, 1 << 20, n[k])
+                ent[n[k]] = (0x7f800000, 0)
+                runs.append(ent)
+            total = sum(n)
+            dst = np.full((total + 2, 2), 0xDEADBEEF, np.uint32)
+            assert dst.ctypes.data % 16 == 0
+            ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+            lib.merge3(ptr(runs[0]), ptr(runs[1]), ptr(runs[2]), offs[0], offs[1], offs[2], total, ptr(dst), trial % 3 == 0)
+            got_x = dst[:total, 0].copy().view(np.float32)
+            want = np.concatenate([np.stack([r[:m, 0].view(np.float32), (r[:m, 1] + o).astype(np.float32), np.full(m, k, np.float32)], 1)
+                                   for k, (r, m, o) in enumerate(zip(runs, n, offs))]) if total else np.zeros((0, 3), np.float32)
+            order = np.lexsort((np.arange(total), want[:, 2], want[:, 0])) if total else []
+            assert np.array_equal(got_x, want[order, 0])
+            assert np.array_equal(dst[:total, 1], want[order, 1].astype(np.uint32))   # ties: earlier run first, order kept inside a run
+            if trial % 3 == 0:
+                assert tuple(dst[total]) == (0x7f800000, 0)
+            else:
+                assert dst[total, 0] == 0xDEADBEEF
+            assert dst[total + 1, 0] == 0xDEADBEEF

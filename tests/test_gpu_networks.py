@@ -1,0 +1,159 @@
+"""Whole networks of the benchmark configurations at reduced batch (and, for the ImageNet-shaped one, reduced
+image size) against the CPU train step through the reference's own CPU operators (oracle/_ref) and through the
+restated oracle; the objective with the reference's constraint cost; and data-parallel gradients against the
+single-shard gradient, on one GPU."""
+import numpy as np
+import pytest
+
+import oracle as O
+from oracle import ref_model
+from tests import parity as P
+
+pytestmark = pytest.mark.gpu
+
+# IMAGENET_CNN's layers on a 64x64 image: same kernels, strides and channel counts, dense input 2*2*512
+IMAGENET_SMALL = [("conv", 3, 64, 7, 2), ("pool", 2),
+                  ("conv", 64, 128, 3, 1), ("conv", 128, 128, 3, 1), ("pool", 2),
+                  ("conv", 128, 256, 3, 1), ("conv", 256, 256, 3, 1), ("pool", 2),
+                  ("conv", 256, 512, 3, 1), ("conv", 512, 512, 3, 1), ("pool", 2),
+                  ("flatten",), ("dense", 2048, 1024), ("dense", 1024, 1000)]
+
+
+def _net_case(name):
+    from snntc_2023_b200 import nets
+    if name == "mnist":
+        return nets.MNIST_MLP, (784,), 10, 24
+    if name == "cifar":
+        return nets.CIFAR_CNN, (32, 32, 3), 10, 2
+    return IMAGENET_SMALL, (64, 64, 3), 1000, 1
+
+
+def _rel_l2(a, b):
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+@pytest.mark.parametrize("name", ["mnist", "cifar", "imagenet64"])
+def test_network_step_against_cpu_train_step(name):
+    """Loss and the flat weight gradient of one train step. Two comparisons, both reported:
+      - against the restated oracle chained layer by layer from the GPU's OWN activations (every layer held to the
+        operator protocol: nothing to amplify), and
+      - end to end against the CPU train step run through the restatement ("port") and through the reference's own
+        CPU operators ("reference"). End to end a single ill-conditioned decision in an early layer changes the
+        inputs of everything behind it, and the reference's CPU gradient code recomputes the denominators from a
+        strict x<y mask (snncvgrad_kernels.cc:55,97-104), so these two are bounded by how far the two CPU runs are
+        from EACH OTHER, not by 1e-4."""
+    import torch
+    from snntc_2023_b200 import nets
+    specs, shape, classes, B = _net_case(name)
+    weights = nets.spec_weights(specs, 31)
+    net = nets.SnnNet(specs, weights=weights, device="cuda")
+    rng = np.random.default_rng(32)
+    x = np.exp(rng.random((B,) + shape)).astype(np.float32)
+    labels = rng.integers(0, classes, B)
+    xd, ld = torch.from_numpy(x).cuda(), torch.from_numpy(labels).cuda()
+
+    # layer by layer: every weighted layer's forward from the GPU's own input to that layer
+    acts = []
+    h = xd
+    with torch.no_grad():
+        for l in net.layers:
+            acts.append(h)
+            h = l(h)
+    wl = 0
+    for l, a in zip(net.layers, acts):
+        if not hasattr(l, "weight"):
+            continue
+        ac = a.cpu().numpy()
+        w = weights[wl]; wl += 1
+        if ac.ndim == 4:
+            p = O.cv_params(l.Kh, l.Kw, l.Sh, l.Sw, "SAME", 1.0)
+            o32, o64 = O.cv_forward(ac, w, p, "f32"), O.cv_forward(ac, w, p, "f64")
+            fan_in = l.Kh * l.Kw * l.C
+        else:
+            p = O.fc_params(biasvolt=1.0)
+            o32, o64 = O.fc_forward(ac, w, p, "f32"), O.fc_forward(ac, w, p, "f64")
+            fan_in = ac.shape[1]
+        with torch.no_grad():
+            y = l(a).cpu().numpy()
+        P.check_forward(y, None, o32, o64, what="%s layer %d forward" % (name, wl), fan_in=fan_in)
+
+    loss = net.loss(xd, ld)
+    net.backward(loss)
+    got = net.flat_grad.cpu().numpy()
+    loss_p, grads_p, _ = ref_model.train_step(specs, weights, x, labels, threads=4, kind="port")
+    want_p = np.concatenate([g.reshape(-1) for g in grads_p])
+    report = {"net": name, "loss_rel_port": abs(float(loss) - loss_p) / abs(loss_p), "grad_rel_l2_port": _rel_l2(got, want_p)}
+    if O.ref_lib() is not None:
+        loss_r, grads_r, _ = ref_model.train_step(specs, weights, x, labels, threads=4, kind="reference")
+        want_r = np.concatenate([g.reshape(-1) for g in grads_r])
+        report.update(loss_rel_reference=abs(float(loss) - loss_r) / abs(loss_r), grad_rel_l2_reference=_rel_l2(got, want_r),
+                      cpu_port_vs_cpu_reference=_rel_l2(want_p, want_r))
+    P.REPORT.append(dict(case="network %s" % name, outputs=0, flagged_frac=0.0, flagged_limit=0.0, over_1e4_frac=0.0,
+                         worst_of_tolerance=0.0, differ_from_fp32=0, max_rel_vs_fp32=0.0, fired=0.0, network=report))
+    print("network parity", report)
+    assert report["loss_rel_port"] <= 1e-4
+    assert report["grad_rel_l2_port"] <= 1e-4, report
+    if "grad_rel_l2_reference" in report:
+        assert report["loss_rel_reference"] <= 1e-4
+        # as close to the reference's CPU operators as the restatement of its GPU kernels is
+        assert report["grad_rel_l2_reference"] <= 1.5 * report["cpu_port_vs_cpu_reference"] + 1e-4, report
+
+
+def test_objective_with_constraint_cost_reaches_the_flat_gradient():
+    """loss_func + constraint_cost as the reference's train_step forms it (snntc-mnist.py:76-80): the operators write
+    their dW into the flat bucket, autograd carries the cost's gradient; SnnNet.backward must leave the SUM there,
+    whichever of the two autograd reaches first."""
+    import torch
+    from snntc_2023_b200 import nets
+    specs = [("conv", 3, 8, 3, 1), ("pool", 2), ("flatten",), ("dense", 8 * 4 * 4, 10)]
+    weights = nets.spec_weights(specs, 5)
+    K, K2 = 100.0, 1e-2
+    rng = np.random.default_rng(6)
+    x = np.exp(rng.random((5, 8, 8, 3))).astype(np.float32)
+    labels = rng.integers(0, 10, 5)
+    xd, ld = torch.from_numpy(x).cuda(), torch.from_numpy(labels).cuda()
+    # expected: operator gradients alone, plus the analytic gradient of the cost
+    net = nets.SnnNet(specs, weights=weights, device="cuda")
+    net.backward(net.loss(xd, ld))
+    ops_only = net.flat_grad.clone()
+    extra = []
+    for w in weights:
+        w64 = torch.from_numpy(w).double().requires_grad_(True)
+        c = K * torch.clamp(1.0 - w64.sum(0), min=0).mean() + K2 * (w64 ** 2).mean()
+        c.backward()
+        extra.append(w64.grad.reshape(-1))
+    want = ops_only.double().cpu() + torch.cat(extra)
+    for order in ("loss_first", "cost_first"):
+        net = nets.SnnNet(specs, weights=weights, device="cuda")
+        loss, cost = net.loss(xd, ld), net.constraint_cost(K, K2)
+        net.backward(loss + cost if order == "loss_first" else cost + loss)
+        got = net.flat_grad.double().cpu()
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-7), order
+        assert all(l.weight.grad.data_ptr() == l.grad_sink.data_ptr() for l in net.weighted_layers())
+    # a second step does not inherit the first one's cost gradient
+    net.backward(net.loss(xd, ld))
+    assert torch.equal(net.flat_grad, ops_only)
+
+
+def test_data_parallel_gradient_equals_full_batch_gradient():
+    """What the all-reduce of a data-parallel step computes, on one GPU: the mean of the shards' flat gradients
+    against the gradient of the whole batch (SURVEY protocol: relative L2 <= 1e-5)."""
+    import torch
+    from snntc_2023_b200 import ddp, nets
+    specs = nets.CIFAR_CNN
+    weights = nets.spec_weights(specs, 41)
+    net = nets.SnnNet(specs, weights=weights, device="cuda")
+    rng = np.random.default_rng(42)
+    B, G = 8, 4
+    x = torch.from_numpy(np.exp(rng.random((B, 32, 32, 3))).astype(np.float32)).cuda()
+    lab = torch.from_numpy(rng.integers(0, 10, B)).cuda()
+    net.backward(net.loss(x, lab))
+    full = net.flat_grad.double().clone()
+    acc = torch.zeros_like(full)
+    for r in range(G):
+        a, b = ddp.shard_bounds(B, r, G)
+        net.backward(net.loss(x[a:b], lab[a:b]))
+        acc += net.flat_grad.double()
+    acc /= G
+    rel = float((acc - full).norm() / full.norm())
+    assert rel <= 1e-5, rel

@@ -22,6 +22,22 @@ CONV_CASES = [
     (50, 1, 5, 5, 1, 1, 1, 1, 1, 1, 1.0, "SAME", "test"),
     (51, 2, 9, 9, 16, 7, 7, 2, 2, 40, 1.0, "SAME", "cfg"),
     (52, 5, 64, 64, 3, 3, 3, 1, 1, 64, 1.0, "SAME", "cfg"),   # 20480 rows: many more than resident warps
+    # the conv layers of the benchmark networks at reduced batch and image size, exact channel counts and fan-in
+    # (577, 1153, 2305, 4609 with the bias row); "ref": reference initialisation, inputs with sentinels
+    (81, 2, 10, 10, 3, 3, 3, 1, 1, 64, 1.0, "SAME", "cfg"),      # first layer: every input spikes
+    (82, 2, 10, 10, 64, 3, 3, 1, 1, 64, 1.0, "SAME", "ref"),
+    (83, 2, 8, 8, 64, 3, 3, 1, 1, 128, 1.0, "SAME", "ref"),
+    (84, 2, 8, 8, 128, 3, 3, 1, 1, 128, 1.0, "SAME", "ref"),
+    (85, 1, 8, 8, 128, 3, 3, 1, 1, 256, 1.0, "SAME", "ref"),
+    (86, 1, 8, 8, 256, 3, 3, 1, 1, 256, 1.0, "SAME", "ref"),
+    (87, 1, 8, 8, 256, 3, 3, 1, 1, 256, 1.0, "SAME", "cfg"),
+    (88, 1, 7, 7, 256, 3, 3, 1, 1, 512, 1.0, "SAME", "ref"),
+    (89, 1, 7, 7, 512, 3, 3, 1, 1, 512, 1.0, "SAME", "ref"),
+    (90, 2, 32, 32, 3, 7, 7, 2, 2, 64, 1.0, "SAME", "cfg"),      # ImageNet-shaped first layer, 7x7 stride 2
+    (91, 2, 32, 32, 64, 3, 3, 1, 1, 128, 0.0, "SAME", "cfg"),    # config 3: 32x32x64 -> 128, no bias
+    (92, 4, 32, 32, 64, 3, 3, 1, 1, 64, 1.0, "SAME", "ref"),     # 4096 rows: the row-skipping dW kernel, several slices
+    (93, 3, 9, 7, 32, 3, 2, 1, 1, 48, 1.0, "VALID", "ref"),      # merged lists with a 3x2 kernel, VALID, odd sizes
+    (94, 2, 6, 9, 20, 2, 3, 1, 1, 12, 0.0, "SAME", "test"),      # 2x3 kernel, asymmetric SAME padding, C not a multiple of 32
 ]
 
 
@@ -33,7 +49,7 @@ def _run_conv(seed, B, H, W, C, Kh, Kw, Sh, Sw, Kc, bv, padding, dist):
     import torch
     from snntc_2023_b200 import ops
     I = Kh * Kw * C
-    x, w = P.make_inputs(seed, (B, H, W, C), (I + (bv > 1e-8), Kc), dist)
+    x, w = P.make_inputs(seed, (B, H, W, C), (I + (bv > 1e-8), Kc), dist, bias=bv > 1e-8)
     params = O.cv_params(Kh, Kw, Sh, Sw, padding, bv)
     xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
     pt, pl, Nh, Nw = ops.conv_geometry(H, W, Kh, Kw, Sh, Sw, padding)
@@ -82,3 +98,74 @@ def test_conv_backward(case):
         rest[:, pt:pt + H, pl:pl + W, :] = 0
         assert float(rest.abs().max()) == 0.0  # padding positions get no gradient
     assert torch.equal(dwp, dw)
+
+
+# ---- kernel variants against each other (measurement build: the kernel choice of a call is given explicitly)
+VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 82, 84, 86, 92, 93, 94)]
+
+
+@pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
+def test_conv_list_builders_agree(case):
+    """Sorted lists by per-field radix sort and by per-pixel sort + merges: the same lists up to the order of equal
+    inputs, which can move the last bits of a sum but not a decision on a well-conditioned output."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    seed, B, H, W, C, Kh, Kw, Sh, Sw, Kc, bv, padding, dist = case
+    x, w, params, xd, wd, out, outc, (pt, pl, Nh, Nw) = _run_conv(*case)
+    a = ops.snn_cv(xd, wd, params, pt, pl, Nh, Nw, opts=_lib.options(list_builder=1)).cpu().numpy()
+    b = ops.snn_cv(xd, wd, params, pt, pl, Nh, Nw, opts=_lib.options(list_builder=2)).cpu().numpy()
+    assert np.array_equal(outc, b), "the default list builder of a 3x3 stride-1 layer is the merging one"
+    fa, fb = a[:B] < 1e5 - 0.1, b[:B] < 1e5 - 0.1
+    assert (fa != fb).sum() <= 1e-4 * fa.size
+    both = fa & fb
+    np.testing.assert_allclose(a[:B][both], b[:B][both], rtol=2e-6, atol=0)
+    # the pre-padded calling convention goes through the same builder
+    xp = O.pad_like_reference(x, Kh, Kw, Sh, Sw, padding)
+    bp = ops.snn_cv(torch.from_numpy(xp).cuda(), wd, params, opts=_lib.options(list_builder=2)).cpu().numpy()
+    assert np.array_equal(bp, b)
+
+
+@pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
+def test_conv_dw_kernels_agree(case):
+    """dW by the dense register-tile kernel and by the row-skipping kernel: the same sums in a different grouping."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    seed, B, H, W, C, Kh, Kw, Sh, Sw, Kc, bv, padding, dist = case
+    if C % 4 or Kc % 4:
+        pytest.skip("the row-skipping kernel needs channel counts that are multiples of 4")
+    x, w, params, xd, wd, out, outc, (pt, pl, Nh, Nw) = _run_conv(*case)
+    g = np.random.default_rng(seed + 2000).standard_normal((B, Nh, Nw, Kc)).astype(np.float32)
+    g[np.random.default_rng(seed).random(g.shape) < 0.5] = 0          # gradients routed through a pooling layer are sparse
+    gd = torch.from_numpy(g).cuda()
+    _, dw1, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=1))
+    dx2, dw2, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
+    ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    P.check_close(dw1.cpu().numpy(), ref["dw"], "dense-tile dW %s" % (case,), abs_sum=ref["dw_abs"])
+    P.check_close(dw2.cpu().numpy(), ref["dw"], "row-skipping dW %s" % (case,), abs_sum=ref["dw_abs"])
+    P.check_close(dx2.cpu().numpy(), ref["dx"], "dX beside the row-skipping dW %s" % (case,), abs_sum=ref["dx_abs"])
+    # twice the same call: no atomics, identical bits
+    _, dw3, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
+    assert torch.equal(dw2, dw3)
+    # values outside the range of the scaled inner loop take the kernel's unscaled loop
+    g[0, 0, 0, :] = 1e36
+    gd = torch.from_numpy(g).cuda()
+    _, dw4, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
+    ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+    with np.errstate(over="ignore", invalid="ignore"):
+        P.check_close(dw4.cpu().numpy(), ref["dw"], "row-skipping dW, unscaled loop %s" % (case,), abs_sum=ref["dw_abs"])
+
+
+def test_conv_inputs_that_never_spike_or_are_not_numbers():
+    """Whole pixels, whole channels and single inputs at MAX: empty pixel runs, empty row runs and empty lists."""
+    import torch
+    from snntc_2023_b200 import ops
+    B, H, W, C, Kc = 2, 7, 6, 32, 16
+    x, w = P.make_inputs(95, (B, H, W, C), (9 * C + 1, Kc), "ref", bias=True)
+    x[0, 2, :, :] = 1e5          # a whole image row
+    x[:, :, :, 5] = 1e5          # a whole channel
+    x[1] = 1e5                   # a whole image: every list empty, only the bias input is left
+    params = O.cv_params(3, 3, 1, 1, "SAME", 1.0)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    out = ops.snn_cv(xd, wd, params, 1, 1, H, W).cpu().numpy()
+    P.check_forward(out[:B], out[B:], O.cv_forward(x, w, params, "f32"), O.cv_forward(x, w, params, "f64"),
+                    rows=P.im2col_rows(x, 3, 3, 1, 1, "SAME"), what="conv with empty lists")

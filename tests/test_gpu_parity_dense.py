@@ -23,13 +23,25 @@ DENSE_CASES = [
     (23, 40, 33, 128, 0.0, "test"),
     (25, 18945, 24, 64, 1.0, "cfg"),    # many more rows than resident warps, odd row count
     (26, 19000, 40, 36, 0.0, "test"),   # the same with a ragged last block of outputs
+    # the dense layers of the benchmark networks at reduced batch, reference initialisation ("ref": inputs with
+    # sentinels as a hidden layer sees them) and the benchmark's own weight family ("cfg")
+    (61, 8, 784, 400, 1.0, "ref"),      # MNIST-shaped MLP
+    (62, 8, 400, 400, 1.0, "ref"),
+    (63, 16, 400, 10, 1.0, "ref"),
+    (64, 4, 4096, 512, 1.0, "ref"),     # CIFAR-shaped net
+    (65, 4, 4096, 512, 1.0, "cfg"),
+    (66, 16, 512, 10, 1.0, "ref"),
+    (67, 2, 25088, 1024, 1.0, "ref"),   # ImageNet-shaped net: CTA-wide sort for the long row
+    (68, 2, 25088, 1024, 1.0, "cfg"),
+    (69, 4, 1024, 1000, 1.0, "ref"),
+    (70, 4, 1024, 1000, 1.0, "cfg"),
 ]
 
 
 def _run_dense(seed, B, I, J, bv, dist):
     import torch
     from snntc_2023_b200 import ops
-    x, w = P.make_inputs(seed, (B, I), (I + (bv > 1e-8), J), dist)
+    x, w = P.make_inputs(seed, (B, I), (I + (bv > 1e-8), J), dist, bias=bv > 1e-8)
     params = O.fc_params(biasvolt=bv)
     dev = torch.device("cuda:0")
     xd, wd = torch.from_numpy(x).to(dev), torch.from_numpy(w).to(dev)
@@ -154,22 +166,73 @@ def test_dense_repeatable():
 
 def test_walk_variants_agree_bit_for_bit():
     """The library picks among several walk kernels (output pairs, consecutive outputs per lane, strided outputs,
-    1/2/4 outputs per lane); forced one by one through the measurement hook they must give identical bits."""
+    1/2/4/8 outputs per lane); forced one by one through the measurement build they must give identical bits."""
     import torch
     from snntc_2023_b200 import _lib, ops
-    lib = _lib.load()
     x, w = P.make_inputs(71, (50, 300), (301, 256), "cfg")
     params = O.fc_params(biasvolt=1.0)
     xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
     ref = ops.snn_fc(xd, wd, params)
-    try:
-        for variant in (1, 2, 3):
-            for jsel in (0, 1, 2, 3):
-                lib.snntc_profile_forward_parts(3 | (jsel << 2) | (variant << 4))
-                out = ops.snn_fc(xd, wd, params)
-                assert torch.equal(out, ref), "variant %d, outputs-per-lane choice %d" % (variant, jsel)
-    finally:
-        lib.snntc_profile_forward_parts(3)
+    for layout in (1, 2, 3):
+        for outputs in (0, 1, 2, 3, 4):
+            out = ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=layout, walk_outputs=outputs))
+            assert torch.equal(out, ref), "layout %d, outputs-per-lane choice %d" % (layout, outputs)
+    # a fan-out that leaves the last block of eight-per-lane outputs partly empty
+    x, w = P.make_inputs(72, (20, 100), (101, 1000), "test")
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    ref = ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=2, walk_outputs=1))
+    for outputs in (2, 3, 4):
+        assert torch.equal(ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=3, walk_outputs=outputs)), ref)
+
+
+def _small_grid_problem(seed, B, I, J, bv, lo, hi):
+    """Inputs and weights on a grid of quarters: every sum of the walk is exact in fp32, so the fp32 restatement IS
+    the reference's result and ties between a spike time and an input are exact, not accidents of rounding."""
+    rng = np.random.default_rng(seed)
+    x = (rng.integers(lo, hi, size=(B, I)) / 4.0).astype(np.float32)
+    w = (rng.integers(-12, 13, size=(I + (bv > 1e-8), J)) / 4.0).astype(np.float32)
+    return x, w
+
+
+@pytest.mark.parametrize("J", [1, 2, 64, 128, 256, 250])
+@pytest.mark.parametrize("bv", [0.0, 1.0])
+def test_dense_exact_ties_between_spike_time_and_next_input(J, bv):
+    """The reference fires when the spike time EQUALS the next input (ysumabs <= x*wsumabs,
+    snntc/snnfc_kernels.cu.cc:46); with small-integer data such ties are exact and frequent (the reference's
+    own tests name them as the source of their mismatches, test-snn-fc-forward.py:74-77). Every walk variant
+    must take the reference's side of the tie."""
+    import torch
+    from snntc_2023_b200 import ops
+    x, w = _small_grid_problem(300 + J, 64, 6, J, bv, 4, 17)        # inputs 1.0 .. 4.0, at or above the bias input
+    params = O.fc_params(biasvolt=bv)
+    out = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params).cpu().numpy()
+    ref = O.fc_forward(x, w, params, "f32")
+    fired_ref = ref["y"] < 1e5 - 0.1
+    # the case really contains ties: outputs whose spike time equals one of the row's inputs
+    ties = (fired_ref & (ref["y"][:, None, :] == x[:, :, None]).any(1)).sum()
+    assert ties > 0
+    assert np.array_equal(out[:64] < 1e5 - 0.1, fired_ref), "fire/no-fire differs on exactly representable data"
+    np.testing.assert_allclose(out[:64][fired_ref], ref["y"][fired_ref], rtol=2e-6, atol=0)
+    np.testing.assert_allclose(out[64:][fired_ref], ref["inv"][fired_ref], rtol=2e-6, atol=0)
+
+
+@pytest.mark.parametrize("J", [2, 64, 128, 256])
+def test_dense_inputs_below_the_bias_input_fire_with_negative_denominator(J):
+    """The reference's tests are sign-safe (snntc/snnfc_kernels.cu.cc:36-38,53-55): with inputs BELOW the bias input
+    an output can arm and fire while sum(w) - theta is negative. Sorted inputs at or above the bias input never get
+    there, but the operator does not check its inputs, so the walk must follow the reference here too."""
+    import torch
+    from snntc_2023_b200 import ops
+    bv = 2.0
+    x, w = _small_grid_problem(400 + J, 96, 5, J, bv, 2, 17)        # inputs 0.5 .. 4.0, bias input at 2.0
+    params = O.fc_params(biasvolt=bv)
+    out = ops.snn_fc(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params).cpu().numpy()
+    ref = O.fc_forward(x, w, params, "f32")
+    fired_ref = ref["y"] < 1e5 - 0.1
+    assert (fired_ref & (ref["inv"] < 0)).sum() >= 5, "the case should contain spikes with a negative denominator"
+    assert np.array_equal(out[:96] < 1e5 - 0.1, fired_ref)
+    np.testing.assert_allclose(out[:96][fired_ref], ref["y"][fired_ref], rtol=2e-6, atol=0)
+    np.testing.assert_allclose(out[96:][fired_ref], ref["inv"][fired_ref], rtol=2e-6, atol=0)
 
 
 def test_dense_unaligned_weight_and_input_pointers():

@@ -118,3 +118,61 @@ def test_inference_forward_is_the_first_half_of_the_training_forward():
     with torch.no_grad():
         y_eval = dense(conv(xin).reshape(2, -1))
     assert torch.equal(y_train.detach(), y_eval)
+
+
+def test_inference_forward_against_the_oracle_and_its_causal_set_histogram():
+    """snntc_fc_infer / snntc_cv_infer held to the forward protocol directly (not through the training forward),
+    and the k histogram against the oracle's count of consumed inputs."""
+    import torch
+    from snntc_2023_b200 import ops
+    # dense, reference tests' distribution: outputs fire early (median k about a third of the fan-in)
+    B, I, J = 48, 300, 200
+    x, w = P.make_inputs(63, (B, I), (I + 1, J), "test")
+    params = O.fc_params(biasvolt=1.0)
+    kh = torch.zeros(I + 2, dtype=torch.int32, device="cuda")
+    y = ops.snn_fc_infer(torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(), params, khist=kh).cpu().numpy()
+    o32, o64 = O.fc_forward(x, w, params, "f32"), O.fc_forward(x, w, params, "f64")
+    P.check_forward(y, None, o32, o64, rows=x, what="dense inference forward")
+    kh = kh.cpu().numpy()
+    assert kh.sum() == B * J
+    fired = o64["y"] < 1e5 - 0.1
+    want = np.bincount(o64["k"][fired], minlength=I + 2)
+    want[I + 1] = (~fired).sum()
+    # outputs the oracle flags as ill-conditioned may land one bin away or in the no-spike bin
+    assert np.abs(kh - want).sum() <= 2 * o64["illc"].sum() + 2
+    assert kh[I + 1] > 0 and kh[:I + 1].sum() > 0
+    # conv, a hidden layer of the benchmark networks
+    Bc, H, W, C, Kc = 2, 8, 8, 64, 64
+    xc, wc = P.make_inputs(64, (Bc, H, W, C), (9 * C + 1, Kc), "ref", bias=True)
+    pc = O.cv_params(3, 3, 1, 1, "SAME", 1.0)
+    khc = torch.zeros(9 * C + 2, dtype=torch.int32, device="cuda")
+    yc = ops.snn_cv_infer(torch.from_numpy(xc).cuda(), torch.from_numpy(wc).cuda(), pc, 1, 1, H, W, khist=khc).cpu().numpy()
+    c32, c64 = O.cv_forward(xc, wc, pc, "f32"), O.cv_forward(xc, wc, pc, "f64")
+    P.check_forward(yc, None, c32, c64, rows=P.im2col_rows(xc, 3, 3, 1, 1, "SAME"), what="conv inference forward")
+    khc = khc.cpu().numpy()
+    firedc = c64["y"] < 1e5 - 0.1
+    wantc = np.bincount(c64["k"][firedc], minlength=9 * C + 2)
+    wantc[9 * C + 1] = (~firedc).sum()
+    assert khc.sum() == firedc.size and np.abs(khc - wantc).sum() <= 2 * c64["illc"].sum() + 2
+
+
+def test_minpool_backward_is_a_gather_for_overlapping_windows():
+    """3x3 windows at stride 1 and 2 overlap: an input can win several windows. The backward sums their gradients
+    in window order (no atomics): two runs give the same bits, and the sum matches numpy."""
+    import torch
+    from snntc_2023_b200 import ops
+    rng = np.random.default_rng(9)
+    for (H, W, K, S) in ((9, 8, 3, 1), (11, 7, 3, 2), (6, 6, 4, 2)):
+        x = np.exp(rng.random((3, H, W, 5))).astype(np.float32)
+        x[rng.random(x.shape) < 0.4] = 1e5
+        xd = torch.from_numpy(x).cuda().requires_grad_(True)
+        y = ops.snn_minpool(xd, K, K, S, S, "SAME")
+        g = torch.randn_like(y)
+        (dx1,) = torch.autograd.grad(y, xd, g, retain_graph=True)
+        (dx2,) = torch.autograd.grad(y, xd, g)
+        assert torch.equal(dx1, dx2)
+        _, arg = O.minpool(x, K, K, S, S, "SAME")
+        want = np.zeros(x.size, np.float64)
+        ok = arg.reshape(-1) >= 0
+        np.add.at(want, arg.reshape(-1)[ok], g.cpu().numpy().reshape(-1)[ok].astype(np.float64))
+        assert np.allclose(dx1.cpu().numpy().reshape(-1), want, rtol=1e-5, atol=1e-6)
