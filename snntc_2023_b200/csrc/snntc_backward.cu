@@ -34,16 +34,10 @@ constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs,
 // of two is exact and (y - x) * scale stays below 1 -- an input below -MAX, a non-zero input or spike value
 // smaller than 2^-60 in magnitude, or a u that is not below 2^100 in magnitude (NaN and inf included).
 // `xin` is the whole input tensor (nx elements). The flag must be zero before the launch.
-// It also fills the twelve constants behind the flag that snn_dw_skip_kernel copies in place of inputs that are
-// not there: MAX x4, {biasvolt, MAX, MAX, MAX}, 0 x4.
 template <bool V4>   // V4: n and nx are multiples of 4 and all pointers 16-byte aligned: 16-byte loads and stores
 __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
                              size_t n, float maxcomp, const float* __restrict__ xin, size_t nx, float maxv,
-                             int* __restrict__ exact_flag, float* __restrict__ consts, float biasvolt) {
-  if (blockIdx.x == 0 && threadIdx.x < 12) {
-    const int t = threadIdx.x;
-    consts[t] = t < 4 ? maxv : (t == 4 ? biasvolt : (t < 8 ? maxv : 0.f));
-  }
+                             int* __restrict__ exact_flag) {
   const float tiny = 8.67361737988e-19f;   // 2^-60
   const float big = 1.26765060023e30f;     // 2^100
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -641,12 +635,23 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     }
 }
 
+// Adds the partial planes of every element in a fixed order (four interleaved running sums, then their sum): the
+// same bits every run, and eight independent loads in flight per thread -- a kernel with a few ten thousand
+// threads and hundreds of planes is bound by load latency otherwise.
 __global__ void snn_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, size_t n, int splits) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
-    float s = 0.f;
-    for (int k = 0; k < splits; ++k) s += partial[(size_t)k * n + e];
-    dw[e] = s;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    int k = 0;
+    for (; k + 8 <= splits; k += 8) {
+      float v[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = __ldcs(partial + (size_t)(k + q) * n + e);
+      s0 += v[0]; s1 += v[1]; s2 += v[2]; s3 += v[3];
+      s0 += v[4]; s1 += v[5]; s2 += v[6]; s3 += v[7];
+    }
+    for (; k < splits; ++k) s0 += __ldcs(partial + (size_t)k * n + e);
+    dw[e] = (s0 + s1) + (s2 + s3);
   }
 }
 
@@ -720,7 +725,6 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return E_WORKSPACE;
   float* uv = static_cast<float*>(ws);
   int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + u_bytes(g));
-  float* consts = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + 64);
   float* planes = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + kFlagBytes);
   // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
   const bool vec = (g.J % 4 == 0) && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)uv) & 15) == 0 &&
@@ -733,8 +737,8 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const size_t nx = g.is_conv ? (size_t)g.B * g.H * g.W * g.C : (size_t)g.R * g.I;
     const bool v4 = (n % 4 == 0) && (nx % 4 == 0) &&
                     (((uintptr_t)grad | (uintptr_t)out | (uintptr_t)uv | (uintptr_t)x) & 15) == 0;
-    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, consts, g.biasvolt);
-    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, consts, g.biasvolt);
+    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
+    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
@@ -770,7 +774,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
       int rps = 0;
       splits = dw_skip_splits(g, li, &rps);
       partial = planes;   // always reduced from the workspace: its tiles are stored 16 bytes at a time
-      rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, consts, li, s);
+      rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, li, s);
       splits = splits < 1 ? 1 : splits;
       if (rc == OK) {
         int blocks = (int)((n + 255) / 256);

@@ -93,11 +93,11 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
                     cudaStream_t s);
 
 // dW by a kernel that skips the (row, output) pairs that did not fire (snntc_dw_skip.cu); conv layers whose
-// channel count is a multiple of 4. `consts` points at {MAX, biasvolt, 0, 0} in device memory (16-byte aligned).
+// channel count is a multiple of 4.
 bool dw_skip_supported(const Geometry& g, const float* x, const float* uv, const float* out);
 int dw_skip_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split);
 int launch_dw_skip(const Geometry& g, const float* uv, const float* x, const float* out, float* partial,
-                   int splits, int rows_per_split, float scale, const int* exact_flag, const float* consts,
+                   int splits, int rows_per_split, float scale, const int* exact_flag,
                    const LaunchInfo& li, cudaStream_t s);
 
 // monotone map float bits -> unsigned so that an unsigned compare orders like the float compare

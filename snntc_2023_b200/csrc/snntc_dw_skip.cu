@@ -14,7 +14,8 @@
 // CTA: 256 threads = 8 warps = 32 output channels; 128*QL fan-in rows; blockIdx.z takes a slice of the rows r.
 // The x tile (16 rows of r at a time, double buffered) is gathered straight from the NHWC image with 16-byte
 // asynchronous copies (four channels of one tap are contiguous), never passing through registers; taps outside
-// the image, rows past the slice and the bias row read small constant vectors instead.
+// the image, rows past the slice and the bias row are plain 16-byte stores of constants (NOT copies from a
+// constant in global memory: every CTA fetching the same 16 bytes makes one L2 line the bottleneck of the kernel).
 #include "snntc_common.cuh"
 
 #include <math_constants.h>
@@ -54,13 +55,11 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// consts: [0..3] = MAX x4 (an input that never spikes), [4..7] = {biasvolt, MAX, MAX, MAX} (the bias row and the
-// padding beside it), [8..11] = 0 x4 (no spike value / no gradient)
 template <int QL>
 __global__ void __launch_bounds__(kThreads, 2)
 snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
                    const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
-                   float scale, const int* __restrict__ exact_flag, const float* __restrict__ consts) {
+                   float scale, const int* __restrict__ exact_flag) {
   constexpr int kTI = 128 * QL;        // fan-in rows per CTA
   constexpr int kCh = 32 * QL;         // 16-byte chunks per row of the x tile
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -82,9 +81,9 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
   const int i0 = blockIdx.y * kTI, j0 = blockIdx.x * kJT;
   const int r_begin = blockIdx.z * rows_per_split;
   const int r_end = min(R, r_begin + rows_per_split);
-  const float* c_never = consts;
-  const float* c_bias = consts + 4;
-  const float* c_zero = consts + 8;
+  // what stands in for inputs that are not there: an input that never spikes; the bias input and the padding beside it
+  const float4 v_never = make_float4(g.maxv, g.maxv, g.maxv, g.maxv);
+  const float4 v_bias = make_float4(g.biasvolt, g.maxv, g.maxv, g.maxv);
 
   for (int q = tid; q < kCh; q += kThreads) {
     const int i = i0 + 4 * q;
@@ -124,16 +123,11 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
       const int rl = e / kCh, q = e - rl * kCh;
       const int4 ri = rowinfo[buf * kRS + rl];
       const int4 ti = tapinfo[q];
-      const float* src = c_never;
-      if (ri.w != 0) {
-        if (ti.w == 1) {
-          if ((unsigned)(ri.y + ti.y) < (unsigned)g.H && (unsigned)(ri.z + ti.z) < (unsigned)g.W)
-            src = x + ((ptrdiff_t)ri.x + ti.x);
-        } else if (ti.w == 2) {
-          src = c_bias;
-        }
-      }
-      cp_async16(xs + rl * kTI + 4 * q, src);
+      float* dst = xs + rl * kTI + 4 * q;
+      const bool in_image = ri.w != 0 && ti.w == 1 && (unsigned)(ri.y + ti.y) < (unsigned)g.H &&
+                            (unsigned)(ri.z + ti.z) < (unsigned)g.W;
+      if (in_image) cp_async16(dst, x + ((ptrdiff_t)ri.x + ti.x));
+      else *reinterpret_cast<float4*>(dst) = (ri.w != 0 && ti.w == 2) ? v_bias : v_never;
     }
     {
       // y and u: 16 rows x 8 chunks each; threads 0..127 fetch y, 128..255 u
@@ -141,9 +135,9 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
       const int rl = h >> 3, cq = h & 7;
       const int r = rb + rl, j = j0 + 4 * cq;
       const float* base = (tid < 128) ? out : uv;
-      const float* src = (r < r_end && j < J) ? base + (size_t)r * J + j : c_zero;
       float* dst = ((tid < 128) ? Ys : Us) + (buf * kRS + rl) * kJT + 4 * cq;
-      cp_async16(dst, src);
+      if (r < r_end && j < J) cp_async16(dst, base + (size_t)r * J + j);
+      else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);   // no spike value, no gradient
     }
     cp_async_commit();
   };
@@ -247,11 +241,11 @@ void plan_tiles(int Itot, int* ntiles, int* ql) {
 
 template <int QL>
 int launch_ql(const Geometry& g, const float* uv, const float* x, const float* out, float* partial, dim3 grid,
-              int rows_per_split, float scale, const int* exact_flag, const float* consts, cudaStream_t s) {
+              int rows_per_split, float scale, const int* exact_flag, cudaStream_t s) {
   const size_t smem = smem_bytes(QL);
   if (cudaFuncSetAttribute(snn_dw_skip_kernel<QL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
     return E_CUDA;
-  snn_dw_skip_kernel<QL><<<grid, kThreads, smem, s>>>(g, uv, x, out, partial, rows_per_split, scale, exact_flag, consts);
+  snn_dw_skip_kernel<QL><<<grid, kThreads, smem, s>>>(g, uv, x, out, partial, rows_per_split, scale, exact_flag);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -282,18 +276,18 @@ int dw_skip_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split)
 }
 
 int launch_dw_skip(const Geometry& g, const float* uv, const float* x, const float* out, float* partial,
-                   int splits, int rows_per_split, float scale, const int* exact_flag, const float* consts,
+                   int splits, int rows_per_split, float scale, const int* exact_flag,
                    const LaunchInfo& li, cudaStream_t s) {
   (void)li;
   int ntiles = 1, ql = 1;
   plan_tiles(g.I + g.has_bias, &ntiles, &ql);
   dim3 grid((g.J + kJT - 1) / kJT, ntiles, splits);
   switch (ql) {
-    case 1: return launch_ql<1>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, consts, s);
-    case 2: return launch_ql<2>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, consts, s);
-    case 3: return launch_ql<3>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, consts, s);
-    case 4: return launch_ql<4>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, consts, s);
-    default: return launch_ql<5>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, consts, s);
+    case 1: return launch_ql<1>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, s);
+    case 2: return launch_ql<2>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, s);
+    case 3: return launch_ql<3>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, s);
+    case 4: return launch_ql<4>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, s);
+    default: return launch_ql<5>(g, uv, x, out, partial, grid, rows_per_split, scale, exact_flag, s);
   }
 }
 

@@ -18,6 +18,7 @@
 //      or outputs lane + 32*m (odd fan-out, unaligned weights).
 #include "snntc_common.cuh"
 
+#include <limits.h>
 #include <math_constants.h>
 
 namespace snntc {
@@ -52,12 +53,10 @@ __device__ __forceinline__ bool ratio_le(float ysum, float wsum, float c) {
   return ya <= c * wa;
 }
 
-// smallest of three floats in one instruction (three-input min of sm_100); a NaN operand is ignored
-__device__ __forceinline__ float fmin3(float a, float b, float c) {
-  float r;
-  asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
+// Smallest of three float bit patterns compared as signed integers. For the sign test of the walk that is all
+// that is needed: the result is <= 0 exactly when one of the floats is negative, -0 or +0 (negative floats are
+// negative integers, +0 is 0, positive floats and NaN patterns with a clear sign bit are positive integers).
+__device__ __forceinline__ int imin3(int a, int b, int c) { return min(min(a, b), c); }
 
 // Number of list entries whose input value lies strictly below y: the causal-set size of an output that fired
 // at y (every consumed input is below the spike value, every other one is not). Binary search, one thread.
@@ -112,7 +111,7 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   // Without bias the sums start at (-theta, 0), for which "ysum/wsum > c" is false for every c >= 0, so the
   // first step needs no special case; with bias the previous input is the bias input itself.
   float xprev = g.has_bias ? g.biasvolt : 0.f;
-  float sticky = CUDART_INF_F;   // -1 while some live output of this lane must be tested exactly at the next step
+  int sticky = INT_MAX;   // INT_MIN while some live output of this lane must be tested exactly at the next step
 
   const float* wl = w + (VECW ? jl[0] : (FULL ? jbase + lane : 0));
   // VECW: addressed by a 32-bit element offset from the (uniform) weight base, widened before the scaling to
@@ -140,21 +139,21 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
 
   // one step for all JPT outputs of this lane: sign test, (rarely) exact test, then consume
   auto step = [&](const float x, const float xprev, const float (&wv)[JPT]) {
-    float q[JPT];
+    int q[JPT];
 #pragma unroll
-    for (int m = 0; m < JPT; ++m) q[m] = fmaf(-x, wsum[m], ysum[m]);
-    float qmin;
-    if constexpr (JPT == 1) qmin = fminf(q[0], sticky);
-    else if constexpr (JPT == 2) qmin = fmin3(q[0], q[1], sticky);
-    else if constexpr (JPT == 4) qmin = fmin3(fmin3(q[0], q[1], q[2]), q[3], sticky);
-    else qmin = fmin3(fmin3(q[0], q[1], q[2]), fmin3(q[3], q[4], q[5]), fmin3(q[6], q[7], sticky));
-    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0.f), 0)) {
+    for (int m = 0; m < JPT; ++m) q[m] = __float_as_int(fmaf(-x, wsum[m], ysum[m]));
+    int qmin;
+    if constexpr (JPT == 1) qmin = min(q[0], sticky);
+    else if constexpr (JPT == 2) qmin = imin3(q[0], q[1], sticky);
+    else if constexpr (JPT == 4) qmin = imin3(imin3(q[0], q[1], q[2]), q[3], sticky);
+    else qmin = imin3(imin3(q[0], q[1], q[2]), imin3(q[3], q[4], q[5]), imin3(q[6], q[7], sticky));
+    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0), 0)) {
       // rare path: the reference's own rounded comparisons for the live outputs concerned (usually one of the
       // lane's outputs in one lane: skip the others with a warp-uniform test each)
       bool again = false;
 #pragma unroll
       for (int m = 0; m < JPT; ++m) {
-        if (JPT > 1 && !__any_sync(0xffffffffu, (q[m] <= 0.f) | (sticky < 0.f))) continue;
+        if (JPT > 1 && !__any_sync(0xffffffffu, (q[m] <= 0) | (sticky < 0))) continue;
         const bool live = livemask[m] != 0;
         const bool fire = live & ratio_gt(ysum[m], wsum[m], xprev) & ratio_le(ysum[m], wsum[m], x);
         if (fire) {
@@ -165,9 +164,9 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
           // q = ysum + x*inf = +inf at every later step
           wsum[m] = -CUDART_INF_F;
         }
-        again |= live & !fire & (q[m] <= 0.f);
+        again |= live & !fire & (q[m] <= 0);
       }
-      sticky = again ? -1.f : CUDART_INF_F;
+      sticky = again ? INT_MIN : INT_MAX;
     }
 #pragma unroll
     for (int m = 0; m < JPT; ++m) {
@@ -240,6 +239,9 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 __device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
+__device__ __forceinline__ void unpack2i(uint64_t v, int& lo, int& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+}
 __device__ __forceinline__ uint64_t sub2(uint64_t a, uint64_t b) {
   uint64_t r;
   asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
@@ -289,17 +291,17 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
 
   const float* wl = w + (FULL ? jbase + 2 * lane : 0);
 
-  float sticky = CUDART_INF_F;   // -1 while some live output of this lane must be tested exactly at the next step
+  int sticky = INT_MAX;   // INT_MIN while some live output of this lane must be tested exactly at the next step
   auto step = [&](const float x, const float xprev, const uint64_t (&wv)[JP]) {
     const uint64_t x2 = pack2(x, x);
-    float q[2 * JP];
+    int q[2 * JP];
 #pragma unroll
-    for (int m = 0; m < JP; ++m) unpack2(fma2(x2, nws[m], ys[m]), q[2 * m], q[2 * m + 1]);
-    float qmin;
-    if constexpr (JP == 1) qmin = fmin3(q[0], q[1], sticky);
-    else if constexpr (JP == 2) qmin = fmin3(fmin3(q[0], q[1], q[2]), q[3], sticky);
-    else qmin = fmin3(fmin3(q[0], q[1], q[2]), fmin3(q[3], q[4], q[5]), fmin3(q[6], q[7], sticky));
-    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0.f), 0)) {
+    for (int m = 0; m < JP; ++m) unpack2i(fma2(x2, nws[m], ys[m]), q[2 * m], q[2 * m + 1]);
+    int qmin;
+    if constexpr (JP == 1) qmin = imin3(q[0], q[1], sticky);
+    else if constexpr (JP == 2) qmin = imin3(imin3(q[0], q[1], q[2]), q[3], sticky);
+    else qmin = imin3(imin3(q[0], q[1], q[2]), imin3(q[3], q[4], q[5]), imin3(q[6], q[7], sticky));
+    if (__builtin_expect(__any_sync(0xffffffffu, qmin <= 0), 0)) {
       // rare path: the reference's own rounded comparisons for the live outputs (see walk_row)
       bool again = false;
 #pragma unroll
@@ -318,11 +320,11 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
             yfin[2 * m + h] = y[h];
             n[h] = CUDART_INF_F;   // ... and park the running weight sum where q stays +inf
           }
-          again |= lv & !fire & (q[2 * m + h] <= 0.f);
+          again |= lv & !fire & (q[2 * m + h] <= 0);
         }
         nws[m] = pack2(n[0], n[1]);
       }
-      sticky = again ? -1.f : CUDART_INF_F;
+      sticky = again ? INT_MIN : INT_MAX;
     }
 #pragma unroll
     for (int m = 0; m < JP; ++m) {
@@ -1004,7 +1006,9 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   const bool al32 = al16 && (g.J % 8 == 0);
   const double cost[4] = {19.0, 24.0, 39.0, 62.0};
   const int ctas[4] = {6, 4, 4, 2};
-  int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : (g.J <= 128 ? 2 : 3)));
+  // (eight outputs per lane exist as a variant but were measured slower than four on every layer of the benchmark
+  // networks -- 1.91 against 1.32 ms on the 2305 x 256 layer: 98 registers, two CTAs per SM -- and are never picked)
+  int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
   int variant = 2;
   if (al8) variant = (g.J <= 64 || jsel < 2) ? 1 : 3;
   if (opt.walk_layout != 0) {

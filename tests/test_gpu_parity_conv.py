@@ -146,8 +146,9 @@ def test_conv_dw_kernels_agree(case):
     # twice the same call: no atomics, identical bits
     _, dw3, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
     assert torch.equal(dw2, dw3)
-    # values outside the range of the scaled inner loop take the kernel's unscaled loop
-    g[0, 0, 0, :] = 1e36
+    # a value outside the range of the scaled inner loop (|u| >= 2^100) sends the kernel through its unscaled loop
+    j_fired = int(np.argmax(outc[0, 0, 0, :] < 1e5 - 0.1))
+    g[0, 0, 0, j_fired] = 4e30
     gd = torch.from_numpy(g).cuda()
     _, dw4, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
     ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
