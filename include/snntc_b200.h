@@ -5,7 +5,8 @@
  * pointer is a DEVICE pointer except the `params*_host` vectors, which are read on the host (the
  * reference pins `params` to host memory as well: snntc/snnfc_kernels.cc:224). The library allocates
  * nothing: outputs and the scratch `workspace` belong to the caller, who sizes the workspace with the
- * matching *_workspace_bytes() call. All work is queued on `stream` (a cudaStream_t passed as void*)
+ * matching *_workspace_bytes() call and aligns it to 256 bytes (what cudaMalloc and every framework allocator
+ * give). All work is queued on `stream` (a cudaStream_t passed as void*)
  * and the call returns without waiting for it; the reference blocks the host after every launch
  * (snntc/snnfc_kernels.cu.cc:187), callers that relied on that must synchronise the stream.
  *
@@ -33,7 +34,7 @@ enum {
   SNNTC_E_SHAPE = -2,      /* a dimension is <= 0 or inconsistent (e.g. grad rows != 2*B) */
   SNNTC_E_WEIGHT_ROWS = -3,/* weight rows != fan-in (+1 when params say bias is on) */
   SNNTC_E_TOO_LARGE = -4,  /* a tensor has more than 2^31-1 elements */
-  SNNTC_E_WORKSPACE = -5,  /* workspace pointer null/misaligned or smaller than *_workspace_bytes() */
+  SNNTC_E_WORKSPACE = -5,  /* workspace pointer null, not 256-byte aligned, or smaller than *_workspace_bytes() */
   SNNTC_E_UNSUPPORTED = -6,/* configuration the kernels cannot run (e.g. fan-in too large for shared memory) */
   SNNTC_E_CUDA = -7,       /* a CUDA runtime call failed; see snntc_last_cuda_error() */
   SNNTC_E_PARAMS = -8      /* params vector holds an invalid kernel size / stride / sentinel */
@@ -215,34 +216,36 @@ SNNTC_API void snntc_set_overlap(int on);
  * Measurement build only (libsnntc_b200_measure.so, compiled with -DSNNTC_MEASURE; the default library does
  * not export these). The four operators with the kernel choice of THE CALL given explicitly, so that a
  * benchmark can time the kernels of an operator apart and a test can check the variants against each other:
- *   opts7 = { forward_parts   bit 0: build the sorted lists, bit 1: walk them (default 3; without bit 1 the
+ *   opts8 = { forward_parts   bit 0: build the sorted lists, bit 1: walk them (default 3; without bit 1 the
  *                             output is not written),
- *             walk_layout     0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane,
+ *             walk_layout     0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane; +4: list
+ *                             entries straight from global memory instead of staged through shared memory,
  *             walk_outputs    0 auto, 1..4: 1, 2, 4, 8 outputs per lane,
  *             list_builder    0 auto, 1 per-row radix sort, 2 per-pixel sort + merges,
  *             backward_parts  bit 0: dX, bit 1: dW (default 3),
  *             dw_kernel       0 auto, 1 dense register tile, 2 row-skipping kernel,
- *             overlap         -1 library setting, 0 one stream, 1 dX beside dW }
- * A null opts7 means the defaults. All variants of a kernel give the same values (the walk variants the same
+ *             overlap         -1 library setting, 0 one stream, 1 dX beside dW,
+ *             dx_kernel       0 auto, 1 dense register tile, 2 list-walking kernel }
+ * A null opts8 means the defaults. All variants of a kernel give the same values (the walk variants the same
  * bits). snntc_fp32_probe queues `ctas` CTAs of 256 threads running `iters` rounds of 8 independent FMAs each
  * and reports the flop count: timed by the caller, it gives the FP32 issue ceiling the kernels are judged against.
  */
 SNNTC_API int snntc_measure_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
                                        int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
-                                       const int* opts7, void* stream);
+                                       const int* opts8, void* stream);
 SNNTC_API int snntc_measure_fc_backward(const float* grad_2BJ, const float* x, const float* w,
                                         const float* params6_host, const float* out_2BJ, float* dx, float* dw,
                                         float* dparams6, int B, int I, int w_rows, int J,
-                                        void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
+                                        void* workspace, size_t workspace_bytes, const int* opts8, void* stream);
 SNNTC_API int snntc_measure_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
                                        int B, int H, int W, int C, int w_rows, int Kc,
                                        int pad_top, int pad_left, int Nh, int Nw,
-                                       void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
+                                       void* workspace, size_t workspace_bytes, const int* opts8, void* stream);
 SNNTC_API int snntc_measure_cv_backward(const float* grad, const float* x_nhwc, const float* w,
                                         const float* params12_host, const float* out, float* dx, float* dw,
                                         float* dparams12, int B, int H, int W, int C, int w_rows, int Kc,
                                         int pad_top, int pad_left, int Nh, int Nw,
-                                        void* workspace, size_t workspace_bytes, const int* opts7, void* stream);
+                                        void* workspace, size_t workspace_bytes, const int* opts8, void* stream);
 SNNTC_API int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream);
 #endif /* SNNTC_MEASURE */
 

@@ -92,9 +92,11 @@ def load_measure():
     return _measure
 
 
-def options(forward_parts=3, walk_layout=0, walk_outputs=0, list_builder=0, backward_parts=3, dw_kernel=0, overlap=-1):
-    """The opts7 vector of the measurement entry points (include/snntc_b200.h)."""
-    return (ctypes.c_int * 7)(forward_parts, walk_layout, walk_outputs, list_builder, backward_parts, dw_kernel, overlap)
+def options(forward_parts=3, walk_layout=0, walk_outputs=0, list_builder=0, backward_parts=3, dw_kernel=0, overlap=-1,
+            dx_kernel=0):
+    """The opts8 vector of the measurement entry points (include/snntc_b200.h)."""
+    return (ctypes.c_int * 8)(forward_parts, walk_layout, walk_outputs, list_builder, backward_parts, dw_kernel, overlap,
+                              dx_kernel)
 
 
 def check(status, what):

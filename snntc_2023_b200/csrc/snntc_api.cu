@@ -155,7 +155,7 @@ int cv_geometry(const float* p, int B, int H, int W, int C, int w_rows, int Kc, 
 
 int check_ws(void* ws, size_t have, size_t need) {
   if (need == 0) return SNNTC_OK;
-  if (!ws || have < need || ((uintptr_t)ws & 15)) return SNNTC_E_WORKSPACE;
+  if (!ws || have < need || ((uintptr_t)ws & 255)) return SNNTC_E_WORKSPACE;
   return SNNTC_OK;
 }
 
@@ -343,14 +343,14 @@ int snntc_cv_backward(const float* grad, const float* x_nhwc, const float* w, co
 
 #ifdef SNNTC_MEASURE
 /* ---- measurement build only: the same operators with the kernel choice of the call given explicitly.
- * opts7 = {forward_parts, walk_layout, walk_outputs, list_builder, backward_parts, dw_kernel, overlap}
+ * opts8 = {forward_parts, walk_layout, walk_outputs, list_builder, backward_parts, dw_kernel, overlap, dx_kernel}
  * (see snntc::Options); a null pointer means the defaults. Nothing here is process-wide state. */
 namespace {
 snntc::Options options_from(const int* o) {
   snntc::Options opt;
   if (o) {
     opt.forward_parts = o[0]; opt.walk_layout = o[1]; opt.walk_outputs = o[2]; opt.list_builder = o[3];
-    opt.backward_parts = o[4]; opt.dw_kernel = o[5]; opt.overlap = o[6];
+    opt.backward_parts = o[4]; opt.dw_kernel = o[5]; opt.overlap = o[6]; opt.dx_kernel = o[7];
   }
   return opt;
 }
@@ -373,32 +373,32 @@ __global__ void __launch_bounds__(256) fp32_probe_kernel(float* sink, int iters,
 
 int snntc_measure_fc_forward(const float* x, const float* w, const float* params6_host, float* out_2BJ,
                              int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
-                             const int* opts7, void* stream) {
+                             const int* opts8, void* stream) {
   return fc_forward_impl(x, w, params6_host, out_2BJ, B, I, w_rows, J, 0, nullptr, workspace, workspace_bytes,
-                         options_from(opts7), stream);
+                         options_from(opts8), stream);
 }
 
 int snntc_measure_fc_backward(const float* grad_2BJ, const float* x, const float* w, const float* params6_host,
                               const float* out_2BJ, float* dx, float* dw, float* dparams6,
                               int B, int I, int w_rows, int J, void* workspace, size_t workspace_bytes,
-                              const int* opts7, void* stream) {
+                              const int* opts8, void* stream) {
   return fc_backward_impl(grad_2BJ, x, w, params6_host, out_2BJ, dx, dw, dparams6, B, I, w_rows, J, workspace,
-                          workspace_bytes, options_from(opts7), stream);
+                          workspace_bytes, options_from(opts8), stream);
 }
 
 int snntc_measure_cv_forward(const float* x_nhwc, const float* w, const float* params12_host, float* out,
                              int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
-                             void* workspace, size_t workspace_bytes, const int* opts7, void* stream) {
+                             void* workspace, size_t workspace_bytes, const int* opts8, void* stream) {
   return cv_forward_impl(x_nhwc, w, params12_host, out, B, H, W, C, w_rows, Kc, pad_top, pad_left, Nh, Nw, 0, nullptr,
-                         workspace, workspace_bytes, options_from(opts7), stream);
+                         workspace, workspace_bytes, options_from(opts8), stream);
 }
 
 int snntc_measure_cv_backward(const float* grad, const float* x_nhwc, const float* w, const float* params12_host,
                               const float* out, float* dx, float* dw, float* dparams12,
                               int B, int H, int W, int C, int w_rows, int Kc, int pad_top, int pad_left, int Nh, int Nw,
-                              void* workspace, size_t workspace_bytes, const int* opts7, void* stream) {
+                              void* workspace, size_t workspace_bytes, const int* opts8, void* stream) {
   return cv_backward_impl(grad, x_nhwc, w, params12_host, out, dx, dw, dparams12, B, H, W, C, w_rows, Kc, pad_top,
-                          pad_left, Nh, Nw, workspace, workspace_bytes, options_from(opts7), stream);
+                          pad_left, Nh, Nw, workspace, workspace_bytes, options_from(opts8), stream);
 }
 
 int snntc_fp32_probe(float* sink, int iters, int ctas, double* flops_out, void* stream) {

@@ -675,8 +675,6 @@ DwPlan plan_dw(const Geometry& g, const LaunchInfo& li) {
 
 }  // namespace
 
-// workspace = u[R,J] (rounded up to 256 bytes), 256 bytes holding the range flag of snn_u_kernel, then the
-// partial dW planes (none when splits == 1)
 static size_t u_bytes(const Geometry& g) { return (((size_t)g.R * g.J * sizeof(float)) + 255) & ~(size_t)255; }
 constexpr size_t kFlagBytes = 256;
 
@@ -703,29 +701,49 @@ static bool want_dw_skip(const Geometry& g, const Options& opt) {
   return g.R >= 2048 && g.I >= 128;
 }
 
-size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) {
+// Where the sparse dX kernel is used: conv layers it supports with enough receptive fields to be worth three launches.
+static bool want_dx_sparse(const Geometry& g, const Options& opt) {
+  if (opt.dx_kernel == 1 || !dx_sparse_shape_ok(g)) return false;
+  if (opt.dx_kernel == 2) return true;
+  return g.R >= 2048 && g.J >= 32;
+}
+
+// workspace = u[R,J] | 256 bytes with the range flag of snn_u_kernel | the partial dW planes (sized for whichever dW
+// kernel needs more; none when neither splits the rows) | the scratch of the sparse dX kernel (conv layers it supports)
+struct BackwardLayout { size_t flag, planes, dx_scratch, total; };
+static BackwardLayout backward_layout(const Geometry& g, const LaunchInfo& li) {
   const size_t plane = (size_t)(g.I + g.has_bias) * (size_t)g.J * sizeof(float);
   const DwPlan p = plan_dw(g, li);
   size_t part = p.splits <= 1 ? 0 : (size_t)p.splits * plane;
   Options any;
   any.dw_kernel = 2;
-  if (want_dw_skip(g, any)) {   // sized for either dW kernel: which one runs also depends on pointer alignment
+  any.dx_kernel = 2;
+  if (want_dw_skip(g, any)) {   // which dW kernel runs also depends on pointer alignment: sized for either
     int rps = 0;
     const size_t skip = (size_t)dw_skip_splits(g, li, &rps) * plane;
     if (skip > part) part = skip;
   }
-  return u_bytes(g) + kFlagBytes + part;
+  BackwardLayout l;
+  l.flag = u_bytes(g);
+  l.planes = l.flag + kFlagBytes;
+  l.dx_scratch = l.planes + ((part + 255) & ~(size_t)255);
+  l.total = l.dx_scratch + (want_dx_sparse(g, any) ? dx_sparse_bytes(g) : 0);
+  return l;
 }
+
+size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li) { return backward_layout(g, li).total; }
 
 int launch_backward(const Geometry& g, const float* grad, const float* x, const float* w, const float* out,
                     float* dx, float* dw, void* ws, size_t ws_bytes, const LaunchInfo& li, const Options& opt,
                     cudaStream_t s) {
   const int Itot = g.I + g.has_bias;
   const int parts = opt.backward_parts;
-  if (!ws || ws_bytes < backward_workspace_bytes(g, li)) return E_WORKSPACE;
+  const BackwardLayout lay = backward_layout(g, li);
+  if (!ws || ws_bytes < lay.total) return E_WORKSPACE;
   float* uv = static_cast<float*>(ws);
-  int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + u_bytes(g));
-  float* planes = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + u_bytes(g) + kFlagBytes);
+  int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + lay.flag);
+  float* planes = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + lay.planes);
+  void* dx_scratch = static_cast<unsigned char*>(ws) + lay.dx_scratch;
   // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
   const bool vec = (g.J % 4 == 0) && (((uintptr_t)out | (uintptr_t)w | (uintptr_t)uv) & 15) == 0 &&
                    (((size_t)g.R * g.J) % 4 == 0);
@@ -754,7 +772,9 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    if (vec && P >= 64 * kWideP && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {   // it stores dx 16 bytes at a time
+    if (want_dx_sparse(g, opt) && dx_sparse_supported(g, x, dx)) {
+      rc = launch_dx_sparse(g, uv, x, w, out, dx, dx_scratch, li, sdx);
+    } else if (vec && P >= 64 * kWideP && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {   // it stores dx 16 bytes at a time
       dim3 gridw((unsigned)((P + kWideP - 1) / kWideP), (CH + kTile - 1) / kTile);
       snn_dx_wide_kernel<<<gridw, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
     } else if (vec) {
@@ -763,7 +783,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
       snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
     }
     count_launch();
-    if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+    if (rc == OK && cudaGetLastError() != cudaSuccess) rc = E_CUDA;
   }
   if (rc == OK && (parts & 2)) {
     const float scale = dw_scale(g);

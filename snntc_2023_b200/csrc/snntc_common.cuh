@@ -35,11 +35,13 @@ struct LaunchInfo {
 // and from the tests that check the variants against each other. Nothing here is process-wide state.
 struct Options {
   int forward_parts = 3;    // bit 0: build the sorted lists, bit 1: walk them
-  int walk_layout = 0;      // 0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane
+  int walk_layout = 0;      // 0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane;
+                            // +4: read list entries straight from global memory instead of through shared memory
   int walk_outputs = 0;     // 0 auto, 1..4: 1, 2, 4, 8 outputs per lane (pairs layout: 2 only)
   int list_builder = 0;     // 0 auto, 1 per-row radix sort, 2 per-pixel sort + merges (3x3 stride-1 conv only)
   int backward_parts = 3;   // bit 0: dX, bit 1: dW
   int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0)
+  int dx_kernel = 0;        // 0 auto, 1 dense register tile, 2 list-walking kernel (conv, C % 4 == 0, C <= 512)
   int overlap = -1;         // -1 library setting (snntc_set_overlap), 0 one stream, 1 dX beside dW
 };
 
@@ -99,6 +101,14 @@ int dw_skip_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split)
 int launch_dw_skip(const Geometry& g, const float* uv, const float* x, const float* out, float* partial,
                    int splits, int rows_per_split, float scale, const int* exact_flag,
                    const LaunchInfo& li, cudaStream_t s);
+
+// dX by a kernel that walks, per input pixel, the lists of outputs with a non-zero gradient factor
+// (snntc_dx_sparse.cu). dx_sparse_bytes is its scratch (lists, their lengths, transposed weights).
+bool dx_sparse_shape_ok(const Geometry& g);
+bool dx_sparse_supported(const Geometry& g, const float* x, const float* dx);
+size_t dx_sparse_bytes(const Geometry& g);
+int launch_dx_sparse(const Geometry& g, const float* uv, const float* x, const float* w, const float* out, float* dx,
+                     void* scratch, const LaunchInfo& li, cudaStream_t s);
 
 // monotone map float bits -> unsigned so that an unsigned compare orders like the float compare
 __host__ __device__ __forceinline__ uint32_t float_to_sortable(float f) {

@@ -81,10 +81,11 @@ __device__ __forceinline__ int entries_below(const WalkEntry* __restrict__ ents,
 // ulp of zero, or a NEGATIVE denominator, which inputs below the bias input can produce and for which the
 // reference fires on the way back up through zero -- makes the lane "sticky": the exact tests run again at
 // the next step whatever q is, until no live output of the lane is in that state any more.
-template <int JPT, int CH, bool FULL, bool VECW>
+template <int JPT, int CH, bool FULL, bool VECW, bool STAGE>
 __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                          const float* __restrict__ w, int jbase, int lane,
-                                         float* __restrict__ y_row, float* __restrict__ inv_row) {
+                                         float* __restrict__ y_row, float* __restrict__ inv_row,
+                                         WalkEntry* __restrict__ sbuf) {
   const int J = g.J;
   int jl[JPT];
   bool jok[JPT];
@@ -175,14 +176,15 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
     }
   };
 
-  int k = 0;
+  // One chunk of CH steps: entries, then their weight rows, then the arithmetic. `fetch(i)` returns entry i of
+  // the part of the list at hand.
   bool all_done = false;
-  for (; k + CH <= nvalid && !all_done; k += CH) {
+  auto chunk = [&](auto fetch, int k0) {
     float xs[CH];
     float wv[CH][JPT];
 #pragma unroll
     for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
+      const WalkEntry e = fetch(k0 + u);
       xs[u] = __uint_as_float(e.x);
       load_weights(e.y, wv[u]);
     }
@@ -193,15 +195,37 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
 #pragma unroll
     for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
     all_done = !__any_sync(0xffffffffu, any_live != 0);
-  }
-  if (!all_done) {
-    for (; k < nvalid; ++k) {
-      const WalkEntry e = __ldcg(ents + k);
-      float wv[JPT];
-      load_weights(e.y, wv);
-      step(__uint_as_float(e.x), xprev, wv);
-      xprev = __uint_as_float(e.x);
+  };
+  auto single = [&](const WalkEntry e) {
+    float wv[JPT];
+    load_weights(e.y, wv);
+    step(__uint_as_float(e.x), xprev, wv);
+    xprev = __uint_as_float(e.x);
+  };
+  if constexpr (STAGE) {
+    // The list goes through shared memory 32 entries at a time: one coalesced read per lane and block, issued a
+    // whole block ahead, instead of one L2 round trip in front of every chunk; a step then reads its entry with
+    // one broadcast shared-memory load. Two buffers of 32 entries per warp.
+    WalkEntry pre = make_uint2(0u, 0u);
+    if (lane < nvalid) pre = __ldcg(ents + lane);
+    int b = 0;
+    for (int base = 0; base < nvalid && !all_done; base += 32, b ^= 32) {
+      sbuf[b + lane] = pre;
+      __syncwarp();
+      if (base + 32 + lane < nvalid) pre = __ldcg(ents + base + 32 + lane);
+      const int nb = min(32, nvalid - base);
+      const WalkEntry* cur = sbuf + b;
+      int kk = 0;
+      for (; kk + CH <= nb && !all_done; kk += CH) chunk([&](int i) { return cur[i]; }, kk);
+      if (!all_done)
+        for (; kk < nb; ++kk) single(cur[kk]);
     }
+  } else {
+    int k = 0;
+    for (; k + CH <= nvalid && !all_done; k += CH)
+      chunk([&](int i) { return __ldcg(ents + i); }, k);   // list entries bypass L1: it is kept for the weights
+    if (!all_done)
+      for (; k < nvalid; ++k) single(__ldcg(ents + k));
   }
 
 #pragma unroll
@@ -260,10 +284,11 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // scalar walk's -- except the sign of an exactly cancelled sum (+0 on both sides), which is why the sum is
 // read back as 0 - nws: 1/(+0) = +inf clamps to "no spike", 1/(-0) would not. Requires J even and the
 // weights 8-byte aligned.
-template <int JP, int CH, bool FULL>
+template <int JP, int CH, bool FULL, bool STAGE>
 __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                           const float* __restrict__ w, int jbase, int lane,
-                                          float* __restrict__ y_row, float* __restrict__ inv_row) {
+                                          float* __restrict__ y_row, float* __restrict__ inv_row,
+                                          WalkEntry* __restrict__ sbuf) {
   const int J = g.J;
   int jl[JP];
   bool jok[JP];
@@ -311,6 +336,8 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
         unpack2(ys[m], y[0], y[1]);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+          // usually one output of one lane is concerned: skip the other half with a warp-uniform test
+          if (!__any_sync(0xffffffffu, (q[2 * m + h] <= 0) | (sticky < 0))) continue;
           const float wsum = 0.f - n[h];   // not -n: an exactly cancelled sum must read +0 as in the scalar walk
           const bool lv = live[2 * m + h] != 0;
           const bool fire = lv & ratio_gt(y[h], wsum, xprev) & ratio_le(y[h], wsum, x);
@@ -337,25 +364,27 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
     return __ldg(reinterpret_cast<const unsigned long long*>(FULL ? wrow + 64 * m : wrow + jl[m]));
   };
 
-  int k = 0;
   bool all_done = false;
-  for (; k + CH <= nvalid && !all_done; k += CH) {
+  auto load_row = [&](unsigned eoff, uint64_t (&wv)[JP]) {
+    if constexpr (JP == 1) {
+      // one pair per lane: a 32-bit element offset from the (uniform) weight base measured faster than a
+      // 64-bit per-lane pointer plus the entry's offset
+      wv[0] = __ldg(reinterpret_cast<const unsigned long long*>(
+          reinterpret_cast<const char*>(w) + (size_t)(eoff + lane_off) * 4u));
+    } else {
+      const float* wrow = wl + eoff;
+#pragma unroll
+      for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
+    }
+  };
+  auto chunk = [&](auto fetch, int k0) {
     float xs[CH];
     uint64_t wv[CH][JP];
 #pragma unroll
     for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = __ldcg(ents + k + u);   // list entries bypass L1: it is kept for the weights
+      const WalkEntry e = fetch(k0 + u);
       xs[u] = __uint_as_float(e.x);
-      if (JP == 1) {
-        // one pair per lane: a 32-bit element offset from the (uniform) weight base measured faster than a
-        // 64-bit per-lane pointer plus the entry's offset
-        wv[u][0] = __ldg(reinterpret_cast<const unsigned long long*>(
-            reinterpret_cast<const char*>(w) + (size_t)(e.y + lane_off) * 4u));
-      } else {
-        const float* wrow = wl + e.y;
-#pragma unroll
-        for (int m = 0; m < JP; ++m) wv[u][m] = load_pair(wrow, m);
-      }
+      load_row(e.y, wv[u]);
     }
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], u == 0 ? xprev : xs[u > 0 ? u - 1 : 0], wv[u]);
@@ -364,17 +393,36 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
 #pragma unroll
     for (int m = 0; m < 2 * JP; ++m) any_live |= live[m];
     all_done = !__any_sync(0xffffffffu, any_live != 0);
-  }
-  if (!all_done) {
-    for (; k < nvalid; ++k) {
-      const WalkEntry e = __ldcg(ents + k);
-      const float* wrow = wl + e.y;
-      uint64_t wv[JP];
+  };
+  auto single = [&](const WalkEntry e) {
+    const float* wrow = wl + e.y;
+    uint64_t wv[JP];
 #pragma unroll
-      for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
-      step(__uint_as_float(e.x), xprev, wv);
-      xprev = __uint_as_float(e.x);
+    for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
+    step(__uint_as_float(e.x), xprev, wv);
+    xprev = __uint_as_float(e.x);
+  };
+  if constexpr (STAGE) {   // the list through shared memory, 32 entries at a time, read a block ahead (see walk_row)
+    WalkEntry pre = make_uint2(0u, 0u);
+    if (lane < nvalid) pre = __ldcg(ents + lane);
+    int b = 0;
+    for (int base = 0; base < nvalid && !all_done; base += 32, b ^= 32) {
+      sbuf[b + lane] = pre;
+      __syncwarp();
+      if (base + 32 + lane < nvalid) pre = __ldcg(ents + base + 32 + lane);
+      const int nb = min(32, nvalid - base);
+      const WalkEntry* cur = sbuf + b;
+      int kk = 0;
+      for (; kk + CH <= nb && !all_done; kk += CH) chunk([&](int i) { return cur[i]; }, kk);
+      if (!all_done)
+        for (; kk < nb; ++kk) single(cur[kk]);
     }
+  } else {
+    int k = 0;
+    for (; k + CH <= nvalid && !all_done; k += CH)
+      chunk([&](int i) { return __ldcg(ents + i); }, k);   // list entries bypass L1: it is kept for the weights
+    if (!all_done)
+      for (; k < nvalid; ++k) single(__ldcg(ents + k));
   }
 
 #pragma unroll
@@ -875,10 +923,12 @@ snn_sort_long_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* _
 }
 
 // Walk kernel: every warp takes (row, block of 32*JPT outputs) items, adjacent warps share a row.
-template <int JPT, bool VECW>
+template <int JPT, bool VECW, bool STAGE>
 __global__ void __launch_bounds__(kFwdThreads)
 snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                 const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
+  __shared__ WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
+  WalkEntry* sbuf = stage + (STAGE ? (threadIdx.x >> 5) * 64 : 0);
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
   const int jchunks = (J + 32 * JPT - 1) / (32 * JPT);
@@ -894,17 +944,20 @@ snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const in
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     if (full_j)
-      walk_row<JPT, CH, true, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row<JPT, CH, true, VECW, STAGE>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr), sbuf);
     else
-      walk_row<JPT, CH, false, VECW>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row<JPT, CH, false, VECW, STAGE>(g, krow, n, w, jc * 32 * JPT, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr), sbuf);
+    if (STAGE) __syncwarp();   // the next row's first block goes into the buffer this row may have read last
   }
 }
 
 // The same items with the outputs of a lane held in pairs (walk_row2): a warp covers 64*JP outputs.
-template <int JP>
+template <int JP, bool STAGE>
 __global__ void __launch_bounds__(kFwdThreads)
 snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                  const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
+  __shared__ WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
+  WalkEntry* sbuf = stage + (STAGE ? (threadIdx.x >> 5) * 64 : 0);
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
   const int jchunks = (J + 64 * JP - 1) / (64 * JP);
@@ -919,39 +972,42 @@ snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const i
     const WalkEntry* krow = keys_g + (size_t)r * istride;
     const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     if (full_j)
-      walk_row2<JP, (JP >= 2 ? 4 : 8), true>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row2<JP, (JP >= 2 ? 4 : 8), true, STAGE>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr), sbuf);
     else
-      walk_row2<JP, (JP >= 2 ? 4 : 8), false>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr));
+      walk_row2<JP, (JP >= 2 ? 4 : 8), false, STAGE>(g, krow, n, w, jc * 64 * JP, lane, y_out + (size_t)r * J, (inv_out ? inv_out + (size_t)r * J : nullptr), sbuf);
+    if (STAGE) __syncwarp();
   }
 }
 
-int key_stride(const Geometry& g) { return (g.I + 1) & ~1; }  // even: rows of keys start 16-byte aligned
+int key_stride(const Geometry& g) { return (g.I + 3) & ~3; }  // a multiple of four entries: rows of keys start 32-byte aligned
 
 size_t keys_bytes(const Geometry& g) { return (size_t)g.R * key_stride(g) * sizeof(u64); }
 size_t nvalid_bytes(const Geometry& g) { return ((size_t)g.R * sizeof(int) + 255) & ~(size_t)255; }
 
 template <int JPT, bool VECW>
 int launch_walk(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
-                const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end) {
+                const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end, bool stage) {
   const int jchunks = (g.J + 32 * JPT - 1) / (32 * JPT);
   const long items = (long)(row_end - row_begin) * jchunks;
   long grid = (items + kFwdWarps - 1) / kFwdWarps;
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
-  snn_walk_kernel<JPT, VECW><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  if (stage) snn_walk_kernel<JPT, VECW, true><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  else snn_walk_kernel<JPT, VECW, false><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
 
 template <int JP>
 int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
-                 const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end) {
+                 const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end, bool stage) {
   const int jchunks = (g.J + 64 * JP - 1) / (64 * JP);
   const long items = (long)(row_end - row_begin) * jchunks;
   long grid = (items + kFwdWarps - 1) / kFwdWarps;
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
-  snn_walk2_kernel<JP><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  if (stage) snn_walk2_kernel<JP, true><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
+  else snn_walk2_kernel<JP, false><<<(int)grid, kFwdThreads, 0, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -1011,24 +1067,25 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   int jsel = pick(32, cost, ctas, g.J <= 32 ? 0 : (g.J <= 64 ? 1 : 2));
   int variant = 2;
   if (al8) variant = (g.J <= 64 || jsel < 2) ? 1 : 3;
-  if (opt.walk_layout != 0) {
-    variant = opt.walk_layout;
+  if ((opt.walk_layout & 3) != 0) {
+    variant = opt.walk_layout & 3;
     if (variant != 2 && !al8) variant = 2;
   }
+  const bool stage = (opt.walk_layout & 4) == 0;   // list entries through shared memory (4: straight from global memory)
   if (opt.walk_outputs != 0) jsel = opt.walk_outputs - 1;
   if (jsel == 3 && !(variant == 3 && al32)) jsel = 2;   // eight outputs per lane exist only as consecutive outputs
   if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (variant == 1) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (variant == 1) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+    if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
     if (variant == 3) {
-      if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-      if (jsel == 2) return launch_walk<4, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-      return launch_walk<8, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+      if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+      if (jsel == 2) return launch_walk<4, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+      return launch_walk<8, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
     }
-    if (jsel == 1) return launch_walk<2, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
-    return launch_walk<4, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1);
+    if (jsel == 1) return launch_walk<2, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+    return launch_walk<4, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
   };
 
   if (use_merge_lists(g, opt)) {

@@ -12,6 +12,8 @@
 //                   the walk kernels read: (x, element offset of weight row ((kh*Kw+kw)*C+c)).
 // A sequential two- or three-way merge costs a few dozen instructions per entry and thread and needs no
 // cooperation between threads; the per-field radix sort it replaces spends about five hundred per entry.
+// Each thread streams through its own runs, so what bounds these kernels is the number of memory transactions:
+// the merges read and write 32 bytes (four entries) at a time.
 // The order among equal input values differs from a per-field sort's; no output can spike between two equal
 // inputs, so the walk's result does not depend on it.
 #include "snntc_common.cuh"
@@ -101,13 +103,38 @@ snn_pixel_runs_kernel(const float* __restrict__ x, int npix, int C, int J, float
   }
 }
 
-__device__ const WalkEntry g_empty_run[2] = {{kRunEndBits, 0u}, {kRunEndBits, 0u}};
+__device__ __align__(32) const WalkEntry g_empty_run[4] = {{kRunEndBits, 0u}, {kRunEndBits, 0u}, {kRunEndBits, 0u}, {kRunEndBits, 0u}};
+
+// How merge3_runs_blocked reaches memory on the device: 32-byte global reads and writes (256-bit accesses of
+// sm_100), and the three four-entry windows of a thread in shared memory, laid out [window][entry][thread] so
+// that a thread's 8-byte accesses always fall into its own pair of banks whatever window and entry it is at.
+struct BlockedMem {
+  uint2* win;   // &windows[0][0][threadIdx.x]; next entry / window kListThreads elements further
+  __device__ __forceinline__ void load_window(int run, const WalkEntry* src) {
+    unsigned v0, v1, v2, v3, v4, v5, v6, v7;
+    asm volatile("ld.global.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3), "=r"(v4), "=r"(v5), "=r"(v6), "=r"(v7) : "l"(src));
+    uint2* w = win + run * 4 * kListThreads;
+    w[0] = make_uint2(v0, v1);
+    w[kListThreads] = make_uint2(v2, v3);
+    w[2 * kListThreads] = make_uint2(v4, v5);
+    w[3 * kListThreads] = make_uint2(v6, v7);
+  }
+  __device__ __forceinline__ WalkEntry window(int run, int k) const { return win[(run * 4 + k) * kListThreads]; }
+  __device__ __forceinline__ void store4(WalkEntry* dst, const WalkEntry (&e)[4]) const {
+    asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 :: "l"(dst), "r"(e[0].x), "r"(e[0].y), "r"(e[1].x), "r"(e[1].y), "r"(e[2].x), "r"(e[2].y), "r"(e[3].x), "r"(e[3].y)
+                 : "memory");
+  }
+};
 
 // One thread per (b, h, nw): merge of the pixel runs (b, h, nw - pad_left + kw), kw < Kw, columns outside the
 // image being empty. Entry offsets gain kw*C*J.
 __global__ void __launch_bounds__(kListThreads)
 snn_row_runs_kernel(const Geometry g, const WalkEntry* __restrict__ pix, const int* __restrict__ pix_n, int pix_stride,
                     WalkEntry* __restrict__ rows, int* __restrict__ rows_n, int row_stride) {
+  __shared__ uint2 windows[3 * 4 * kListThreads];
+  BlockedMem mem = {windows + threadIdx.x};
   const int total_threads = g.B * g.H * g.Nw;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= total_threads) return;
@@ -126,8 +153,8 @@ snn_row_runs_kernel(const Geometry g, const WalkEntry* __restrict__ pix, const i
     }
     off[kw] = (uint32_t)kw * (uint32_t)g.C * (uint32_t)g.J;
   }
-  merge3_runs<WalkEntry, uint4>(run[0], run[1], run[2], off[0], off[1], off[2], total,
-                                rows + (size_t)t * row_stride, true);
+  merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total,
+                                             rows + (size_t)t * row_stride, true, mem);
   rows_n[t] = total;
 }
 
@@ -136,6 +163,8 @@ snn_row_runs_kernel(const Geometry g, const WalkEntry* __restrict__ pix, const i
 __global__ void __launch_bounds__(kListThreads)
 snn_field_lists_kernel(const Geometry g, const WalkEntry* __restrict__ rows, const int* __restrict__ rows_n,
                        int row_stride, WalkEntry* __restrict__ lists, int* __restrict__ nvalid, int istride) {
+  __shared__ uint2 windows[3 * 4 * kListThreads];
+  BlockedMem mem = {windows + threadIdx.x};
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= g.R) return;
   const int nw = r % g.Nw;
@@ -155,13 +184,14 @@ snn_field_lists_kernel(const Geometry g, const WalkEntry* __restrict__ rows, con
     }
     off[kh] = (uint32_t)kh * (uint32_t)g.Kw * (uint32_t)g.C * (uint32_t)g.J;
   }
-  merge3_runs<WalkEntry, uint4>(run[0], run[1], run[2], off[0], off[1], off[2], total,
-                                lists + (size_t)r * istride, false);
+  merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total,
+                                             lists + (size_t)r * istride, false, mem);
   nvalid[r] = total;
 }
 
-int pixel_stride(const Geometry& g) { return (g.C + 2 + 1) & ~1; }            // entries per pixel run, even
-int row_stride(const Geometry& g) { return (g.Kw * g.C + 2 + 1) & ~1; }       // entries per row run, even
+// entries per pixel run and per row run: room for the terminator, rounded up to four entries (32 bytes)
+int pixel_stride(const Geometry& g) { return (g.C + 1 + 3) & ~3; }
+int row_stride(const Geometry& g) { return (g.Kw * g.C + 1 + 3) & ~3; }
 size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 struct MergeScratch { size_t pix, pix_n, rows, rows_n, total; };

@@ -68,4 +68,53 @@ SNNTC_HD void merge3_runs(const Entry* __restrict__ a, const Entry* __restrict__
   }
 }
 
+// The same merge moving four entries (32 bytes) per memory transaction: a thread that reads and writes 8 bytes at
+// a time touches a different 32-byte sector with every access, so a warp's load or store is 32 sector
+// transactions for 256 useful bytes. Here every run is read through a four-entry window (refilled by one 32-byte
+// read whenever the position crosses a multiple of four) and the output leaves four entries at a time.
+//   Mem::load_window(run, src)   copies entries src[0..4) into window `run` (0..2); src is 32-byte aligned
+//   Mem::window(run, k)          entry k of window `run`
+//   Mem::store4(dst, e)          writes e[0..4) to dst[0..4); dst is 32-byte aligned
+// Runs, dst and the empty run must be 32-byte aligned and readable / writable up to the next multiple of four
+// entries past their terminator (past `total` for dst): the last group is written whole, whatever lies behind
+// `total` in it is unspecified.
+template <typename Entry, typename Mem>
+SNNTC_HD void merge3_runs_blocked(const Entry* __restrict__ a, const Entry* __restrict__ b, const Entry* __restrict__ c,
+                                  uint32_t off_a, uint32_t off_b, uint32_t off_c, int total, Entry* __restrict__ dst,
+                                  bool terminate, Mem& mem) {
+  mem.load_window(0, a);
+  mem.load_window(1, b);
+  mem.load_window(2, c);
+  Entry ha = mem.window(0, 0), hb = mem.window(1, 0), hc = mem.window(2, 0);
+  uint32_t pa = 0, pb = 0, pc = 0;
+  for (int k0 = 0; k0 < total; k0 += 4) {
+    Entry out[4];
+#if defined(__CUDA_ARCH__)
+#pragma unroll
+#endif
+    for (int u = 0; u < 4; ++u) {
+      out[u].x = 0; out[u].y = 0;
+      if (k0 + u < total) {
+        const float fa = entry_value(ha.x), fb = entry_value(hb.x), fc = entry_value(hc.x);
+        const bool sa = (fa <= fb) & (fa <= fc);
+        const bool sb = !sa & (fb <= fc);
+        out[u].x = sa ? ha.x : (sb ? hb.x : hc.x);
+        out[u].y = (sa ? ha.y : (sb ? hb.y : hc.y)) + (sa ? off_a : (sb ? off_b : off_c));
+        const Entry* run = sa ? a : (sb ? b : c);
+        const int which = sa ? 0 : (sb ? 1 : 2);
+        const uint32_t pos = (sa ? pa : (sb ? pb : pc)) + 1u;
+        if ((pos & 3u) == 0u) mem.load_window(which, run + pos);
+        const Entry next = mem.window(which, (int)(pos & 3u));   // at worst the run's terminator
+        if (sa) { ha = next; pa = pos; } else if (sb) { hb = next; pb = pos; } else { hc = next; pc = pos; }
+      }
+    }
+    mem.store4(dst + k0, out);
+  }
+  if (terminate) {
+    Entry end;
+    end.x = kRunEndBits; end.y = 0;
+    dst[total] = end;
+  }
+}
+
 }  // namespace snntc

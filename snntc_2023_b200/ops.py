@@ -89,7 +89,7 @@ def conv_geometry(H, W, Kh, Kw, Sh, Sw, padding):
 
 
 # ------------------------------------------------------------------------------------------ raw ops
-# `opts` (an opts7 vector from _lib.options) selects kernels explicitly through the measurement build of the
+# `opts` (an opts8 vector from _lib.options) selects kernels explicitly through the measurement build of the
 # library; `workspace` lets a caller keep the scratch between two calls (lists built by one, walked by the next).
 def snn_fc(inp, weight, params, opts=None, workspace=None, out=None):
     x = _as_cuda_f32(inp, "in"); w = _as_cuda_f32(weight, "weight"); p = _params(params, 6)

@@ -80,8 +80,8 @@ def test_validation_status_codes_without_a_device():
     assert lib.snntc_fc_forward_workspace_bytes(256, 784, 400) >= 256 * 784 * 8
     assert lib.snntc_fc_backward_workspace_bytes(1, 25088, 25089, 1024) == 4096 + 256   # u[1,1024] and the range flag: enough tiles, no row split
     # a 3x3 stride-1 convolution also gets the scratch of the merging list builder; a 5x5 one does not
-    lists = 2 * 8 * 8 * 290 * 8
-    assert lib.snntc_cv_forward_workspace_bytes(2, 8, 8, 32, 16, 3, 3, 8, 8) > lists + 2 * 8 * 8 * 34 * 8
+    lists = 2 * 8 * 8 * 288 * 8
+    assert lib.snntc_cv_forward_workspace_bytes(2, 8, 8, 32, 16, 3, 3, 8, 8) > lists + 2 * 8 * 8 * 36 * 8
     assert lib.snntc_cv_forward_workspace_bytes(2, 8, 8, 32, 16, 5, 5, 8, 8) < 2 * 8 * 8 * 802 * 8 + 4096
 
 
@@ -169,9 +169,20 @@ def test_sequential_merge_of_sorted_runs_on_the_host():
 struct uint2 { unsigned x, y; };
 struct uint4 { unsigned x, y, z, w; };
 #include "%s"
+struct HostMem {
+  uint2 w[3][4];
+  void load_window(int run, const uint2* src) { memcpy(w[run], src, sizeof(w[run])); }
+  uint2 window(int run, int k) const { return w[run][k]; }
+  void store4(uint2* dst, const uint2 (&e)[4]) const { memcpy(dst, e, sizeof(e)); }
+};
 extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned oa, unsigned ob, unsigned oc,
-                       int total, uint2* dst, int terminate) {
-  snntc::merge3_runs<uint2, uint4>(a, b, c, oa, ob, oc, total, dst, terminate != 0);
+                       int total, uint2* dst, int terminate, int blocked) {
+  if (blocked) {
+    HostMem mem;
+    snntc::merge3_runs_blocked<uint2, HostMem>(a, b, c, oa, ob, oc, total, dst, terminate != 0, mem);
+  } else {
+    snntc::merge3_runs<uint2, uint4>(a, b, c, oa, ob, oc, total, dst, terminate != 0);
+  }
 }
 """ % os.path.join(ROOT, "snntc_2023_b200", "csrc", "snntc_merge.cuh")
     with tempfile.TemporaryDirectory() as d:
@@ -180,21 +191,24 @@ extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned 
         subprocess.check_call(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-o", so, cpp])
         lib = ctypes.CDLL(so)
         rng = np.random.default_rng(0)
-        for trial in range(200):
+        for trial in range(400):
+            blocked = trial >= 200     # the variant that moves four entries per access: runs padded to four entries
             n = [int(rng.integers(0, 40)) if rng.random() > 0.2 else 0 for _ in range(3)]
             runs, offs = [], [int(rng.integers(0, 1000)) for _ in range(3)]
             for k in range(3):
                 vals = np.sort(np.round(np.exp(rng.random(n[k]) * 2), 1 if trial % 2 else 6).astype(np.float32))   # odd trials: many ties
-                ent = np.zeros((n[k] + 1, 2), np.uint32)
+                cap = (n[k] + 1 + 3) // 4 * 4
+                ent = np.full((cap, 2), 0x12345678, np.uint32)        # whatever lies behind the terminator is never used
                 ent[:n[k], 0] = vals.view(np.uint32)
                 ent[:n[k], 1] = rng.integers(0, 1 << 20, n[k])
                 ent[n[k]] = (0x7f800000, 0)
                 runs.append(ent)
             total = sum(n)
-            dst = np.full((total + 2, 2), 0xDEADBEEF, np.uint32)
+            dst = np.full(((total + 1 + 3) // 4 * 4 + 4, 2), 0xDEADBEEF, np.uint32)
             assert dst.ctypes.data % 16 == 0
             ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
-            lib.merge3(ptr(runs[0]), ptr(runs[1]), ptr(runs[2]), offs[0], offs[1], offs[2], total, ptr(dst), trial % 3 == 0)
+            lib.merge3(ptr(runs[0]), ptr(runs[1]), ptr(runs[2]), offs[0], offs[1], offs[2], total, ptr(dst), trial % 3 == 0,
+                       int(blocked))
             got_x = dst[:total, 0].copy().view(np.float32)
             want = np.concatenate([np.stack([r[:m, 0].view(np.float32), (r[:m, 1] + o).astype(np.float32), np.full(m, k, np.float32)], 1)
                                    for k, (r, m, o) in enumerate(zip(runs, n, offs))]) if total else np.zeros((0, 3), np.float32)
@@ -203,6 +217,9 @@ extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned 
             assert np.array_equal(dst[:total, 1], want[order, 1].astype(np.uint32))   # ties: earlier run first, order kept inside a run
             if trial % 3 == 0:
                 assert tuple(dst[total]) == (0x7f800000, 0)
-            else:
+            elif not blocked:
                 assert dst[total, 0] == 0xDEADBEEF
-            assert dst[total + 1, 0] == 0xDEADBEEF
+            if not blocked:
+                assert dst[total + 1, 0] == 0xDEADBEEF
+            else:   # whole groups of four are written, nothing behind the last group
+                assert np.all(dst[(total + 3) // 4 * 4 + (1 if (trial % 3 == 0 and total % 4 == 0) else 0):, 0] == 0xDEADBEEF)

@@ -38,6 +38,7 @@ CONV_CASES = [
     (92, 4, 32, 32, 64, 3, 3, 1, 1, 64, 1.0, "SAME", "ref"),     # 4096 rows: the row-skipping dW kernel, several slices
     (93, 3, 9, 7, 32, 3, 2, 1, 1, 48, 1.0, "VALID", "ref"),      # merged lists with a 3x2 kernel, VALID, odd sizes
     (94, 2, 6, 9, 20, 2, 3, 1, 1, 12, 0.0, "SAME", "test"),      # 2x3 kernel, asymmetric SAME padding, C not a multiple of 32
+    (96, 2, 11, 9, 16, 3, 3, 2, 1, 24, 1.0, "SAME", "test"),     # strides 2x1: the list-walking dX kernel with strided taps
 ]
 
 
@@ -101,7 +102,7 @@ def test_conv_backward(case):
 
 
 # ---- kernel variants against each other (measurement build: the kernel choice of a call is given explicitly)
-VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 82, 84, 86, 92, 93, 94)]
+VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 51, 82, 84, 86, 92, 93, 94, 96)]
 
 
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
@@ -154,6 +155,33 @@ def test_conv_dw_kernels_agree(case):
     ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
     with np.errstate(over="ignore", invalid="ignore"):
         P.check_close(dw4.cpu().numpy(), ref["dw"], "row-skipping dW, unscaled loop %s" % (case,), abs_sum=ref["dw_abs"])
+
+
+@pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
+def test_conv_dx_kernels_agree(case):
+    """dX by the dense register-tile kernels and by the kernel that walks the lists of outputs with a gradient: the
+    same terms added in the same order (the skipped ones are zeros), hence the same bits."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    seed, B, H, W, C, Kh, Kw, Sh, Sw, Kc, bv, padding, dist = case
+    if C % 4 or C < 16:
+        pytest.skip("the list-walking kernel needs a channel count that is a multiple of 4, at least 16")
+    x, w, params, xd, wd, out, outc, (pt, pl, Nh, Nw) = _run_conv(*case)
+    for zero_share in (0.0, 0.8):
+        g = np.random.default_rng(seed + 3000).standard_normal((B, Nh, Nw, Kc)).astype(np.float32)
+        g[np.random.default_rng(seed + 1).random(g.shape) < zero_share] = 0
+        gd = torch.from_numpy(g).cuda()
+        dx1, _, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dx_kernel=1))
+        dx2, dw2, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dx_kernel=2))
+        ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
+        P.check_close(dx2.cpu().numpy(), ref["dx"], "list-walking dX %s" % (case,), abs_sum=ref["dx_abs"])
+        P.check_close(dw2.cpu().numpy(), ref["dw"], "dW beside the list-walking dX %s" % (case,), abs_sum=ref["dw_abs"])
+        assert torch.equal(dx1, dx2), "dense and list-walking dX differ in bits"
+    # the pre-padded calling convention: padding pixels hold MAX and get a zero gradient
+    xp = torch.from_numpy(O.pad_like_reference(x, Kh, Kw, Sh, Sw, padding)).cuda()
+    a, _, _ = ops.snn_cv_grad(gd, xp, wd, params, out, opts=_lib.options(dx_kernel=1))
+    b, _, _ = ops.snn_cv_grad(gd, xp, wd, params, out, opts=_lib.options(dx_kernel=2))
+    assert torch.equal(a, b)
 
 
 def test_conv_inputs_that_never_spike_or_are_not_numbers():

@@ -173,7 +173,7 @@ def test_walk_variants_agree_bit_for_bit():
     params = O.fc_params(biasvolt=1.0)
     xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
     ref = ops.snn_fc(xd, wd, params)
-    for layout in (1, 2, 3):
+    for layout in (1, 2, 3, 5, 6, 7):      # 5..7: the same layouts reading list entries straight from global memory
         for outputs in (0, 1, 2, 3, 4):
             out = ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=layout, walk_outputs=outputs))
             assert torch.equal(out, ref), "layout %d, outputs-per-lane choice %d" % (layout, outputs)
