@@ -635,6 +635,111 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
     }
 }
 
+// ------------------------------------------------------------------------------------------- dW, small fan-in
+// At most 32 weight rows (the first convolution of an image network: 3x3x3 + bias = 28): the 128-row tile of
+// snn_dw_kernel would be three quarters padding. Here lane i of every warp owns weight row i and warp w the JB
+// outputs w*JB .. w*JB+JB-1 (J = 8*JB), accumulators in registers; a CTA walks a slice of the rows r. Whether output
+// (r,j) carries a gradient is the same question for all lanes, so rows without one are skipped by a warp-uniform
+// branch. Same arithmetic per element as the other dW kernels (saturating FMA of the scaled difference, FMA with
+// -u/s), same exactness rule.
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+  float r;
+  asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+template <int JB>
+__global__ void __launch_bounds__(kBwdThreads)
+snn_dw_small_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
+                    const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
+                    float scale, const int* __restrict__ exact_flag) {
+  const int J = g.J, I = g.I, R = g.R;
+  const int Itot = I + g.has_bias;
+  const bool fast = scale != 1.0f && __ldg(exact_flag) == 0;
+  const float sc = fast ? scale : 1.0f;
+  const float nsc = -sc;
+  const float nusc = fast ? -1.0f / scale : -1.0f;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j0 = warp * JB;
+  const int r_begin = blockIdx.z * rows_per_split;
+  const int r_end = min(R, r_begin + rows_per_split);
+  // this lane's input: tap (kh, kw, c) of the receptive field, or the bias input, or nothing
+  int l_kh = 0, l_kw = 0, l_off = 0;
+  if (g.is_conv && lane < I) {
+    const int tap = lane / g.C, c = lane - tap * g.C;
+    l_kh = tap / g.Kw;
+    l_kw = tap - l_kh * g.Kw;
+    l_off = (l_kh * g.W + l_kw) * g.C + c;
+  }
+  float acc[JB];
+#pragma unroll
+  for (int q = 0; q < JB; ++q) acc[q] = 0.f;
+
+  for (int r = r_begin; r < r_end; ++r) {
+    float4 u4[JB / 4];
+    const float4* up = reinterpret_cast<const float4*>(uv + (size_t)r * J + j0);
+    bool any = false;
+#pragma unroll
+    for (int q = 0; q < JB / 4; ++q) {
+      u4[q] = __ldg(up + q);
+      any |= (u4[q].x != 0.f) | (u4[q].y != 0.f) | (u4[q].z != 0.f) | (u4[q].w != 0.f);
+    }
+    if (!any) continue;   // warp-uniform: every lane read the same values
+    float xv = g.maxv;    // a lane without an input, or a tap outside the image: never spikes
+    if (lane == I && g.has_bias) {
+      xv = g.biasvolt;
+    } else if (lane < I) {
+      if (!g.is_conv) {
+        xv = __ldg(x + (size_t)r * I + lane);
+      } else {
+        const int nw = r % g.Nw;
+        const int t = r / g.Nw;
+        const int nh = t % g.Nh;
+        const int b = t / g.Nh;
+        const int h0 = nh * g.Sh - g.pad_top, w0 = nw * g.Sw - g.pad_left;
+        if ((unsigned)(h0 + l_kh) < (unsigned)g.H && (unsigned)(w0 + l_kw) < (unsigned)g.W)
+          xv = __ldg(x + ((ptrdiff_t)(b * g.H + h0) * g.W + w0) * g.C + l_off);
+      }
+    }
+    const float4* yp = reinterpret_cast<const float4*>(out + (size_t)r * J + j0);
+#pragma unroll
+    for (int q = 0; q < JB / 4; ++q) {
+      const float uu[4] = {u4[q].x, u4[q].y, u4[q].z, u4[q].w};
+      if (uu[0] == 0.f && uu[1] == 0.f && uu[2] == 0.f && uu[3] == 0.f) continue;
+      const float4 y4 = __ldg(yp + q);
+      const float yy[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        // (a zero u adds +-0: no need to branch inside a group of four)
+        const float t = fast ? fma_sat(xv, nsc, yy[k] * sc) : fmaxf(yy[k] - xv, 0.f);
+        acc[4 * q + k] = fmaf(t, uu[k] * nusc, acc[4 * q + k]);
+      }
+    }
+  }
+  if (lane < Itot) {
+    float* dst = partial + (size_t)blockIdx.z * Itot * J + (size_t)lane * J + j0;
+#pragma unroll
+    for (int q = 0; q < JB; ++q) dst[q] = acc[q];
+  }
+}
+
+static bool dw_small_ok(const Geometry& g, const float* uv, const float* out) {
+  const int Itot = g.I + g.has_bias;
+  if (Itot > 32 || g.R < 4096) return false;
+  if (g.J != 32 && g.J != 64 && g.J != 128 && g.J != 256) return false;
+  if (g.is_conv && (long long)g.B * g.H * g.W * g.C > 0x7fffffffLL) return false;
+  return (((uintptr_t)uv | (uintptr_t)out) & 15) == 0;
+}
+static int dw_small_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split) {
+  long want = 4L * li.num_sms;
+  const long max_splits = ((long)g.R + 63) / 64;
+  if (want > max_splits) want = max_splits;
+  if (want < 1) want = 1;
+  const long rps = ((long)g.R + want - 1) / want;
+  *rows_per_split = (int)rps;
+  return (int)(((long)g.R + rps - 1) / rps);
+}
+
 // Adds the partial planes of every element in a fixed order (four interleaved running sums, then their sum): the
 // same bits every run, and eight independent loads in flight per thread -- a kernel with a few ten thousand
 // threads and hundreds of planes is bound by load latency otherwise.
@@ -723,6 +828,11 @@ static BackwardLayout backward_layout(const Geometry& g, const LaunchInfo& li) {
     const size_t skip = (size_t)dw_skip_splits(g, li, &rps) * plane;
     if (skip > part) part = skip;
   }
+  if (g.I + g.has_bias <= 32 && g.R >= 4096) {   // the small fan-in kernel
+    int rps = 0;
+    const size_t small = (size_t)dw_small_splits(g, li, &rps) * plane;
+    if (small > part) part = small;
+  }
   BackwardLayout l;
   l.flag = u_bytes(g);
   l.planes = l.flag + kFlagBytes;
@@ -796,6 +906,24 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
       partial = planes;   // always reduced from the workspace: its tiles are stored 16 bytes at a time
       rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, li, s);
       splits = splits < 1 ? 1 : splits;
+      if (rc == OK) {
+        int blocks = (int)((n + 255) / 256);
+        if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;
+        snn_dw_reduce_kernel<<<blocks, 256, 0, s>>>(partial, dw, n, splits);
+        count_launch();
+        if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+      }
+    } else if (opt.dw_kernel != 1 && dw_small_ok(g, uv, out)) {
+      int rps = 0;
+      splits = dw_small_splits(g, li, &rps);
+      partial = planes;
+      dim3 grid(1, 1, splits);
+      if (g.J == 32) snn_dw_small_kernel<4><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, rps, scale, exact_flag);
+      else if (g.J == 64) snn_dw_small_kernel<8><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, rps, scale, exact_flag);
+      else if (g.J == 128) snn_dw_small_kernel<16><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, rps, scale, exact_flag);
+      else snn_dw_small_kernel<32><<<grid, kBwdThreads, 0, s>>>(g, uv, x, out, partial, rps, scale, exact_flag);
+      count_launch();
+      if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
       if (rc == OK) {
         int blocks = (int)((n + 255) / 256);
         if (blocks > 4 * li.num_sms) blocks = 4 * li.num_sms;

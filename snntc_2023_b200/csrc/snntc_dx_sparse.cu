@@ -11,9 +11,10 @@
 //   2. snn_weight_transpose_kernel lays the weights out as Wt[tap][j][c], so that the C weights one list entry needs
 //      for one tap are contiguous;
 //   3. snn_dx_sparse_kernel keeps an input pixel's channels in registers (CPL per lane, C / CPL lanes per pixel),
-//      visits the receptive fields that cover the pixel tap by tap and walks their lists: per entry one 16-byte list
-//      read, 16-byte weight reads and a compare + predicated FMA per channel. Pixel-stationary as the dense kernel:
-//      no atomics (the reference scatters with atomicAdd, snncvgrad_kernels.cu.cc:83).
+//      gathers the lists of the receptive fields that cover the pixel, tap by tap, into shared memory and walks them:
+//      per entry one broadcast shared-memory read, 16-byte weight reads and a compare + predicated FMA per channel.
+//      Pixel-stationary as the dense kernel: no atomics (the reference scatters with atomicAdd,
+//      snncvgrad_kernels.cu.cc:83).
 // The terms of a sum are added in the same order as in the dense kernel (tap-major, j ascending; the skipped ones
 // are +-0), so the two kernels give the same bits.
 #include "snntc_common.cuh"
@@ -71,20 +72,34 @@ __device__ __forceinline__ void masked_fma(float& acc, float x, float y, float u
 }
 
 // CPL channels per lane (4, 8 or 16), LPP lanes per pixel (a power of two, LPP * CPL >= C): a warp holds
-// 32 / LPP input pixels at a time.
+// PPW = 32 / LPP input pixels at a time.
+//
+// The lists a pixel needs (one per tap that an output reads it through) are first copied into shared memory by
+// the pixel's own lanes, back to back and with the tap folded into the entry (its third word becomes the element
+// offset of weight row (tap, j) in Wt), kStage / PPW entries per pixel and round. The arithmetic then runs over
+// that flat sequence: one broadcast shared-memory read per entry instead of a global read in front of every
+// weight read, and one loop instead of one per tap.
+constexpr int kStage = 256;   // staged list entries per warp and round
+
 template <int CPL, int LPP>
 __global__ void __launch_bounds__(kThreads)
 snn_dx_sparse_kernel(const Geometry g, const float* __restrict__ x, const float* __restrict__ wt,
                      const uint4* __restrict__ list, const int* __restrict__ count, float* __restrict__ dx) {
   constexpr int PPW = 32 / LPP;                       // pixels per warp
+  constexpr int SB = kStage / PPW;                    // staged entries per pixel and round
+  constexpr int UN = CPL <= 4 ? 4 : 2;                // entries whose weight reads are in flight together
+  __shared__ uint4 stage_all[(kThreads / 32) * kStage];
   const int lane = threadIdx.x & 31;
   const int sub = lane / LPP;                         // which of the warp's pixels
-  const int c0 = (lane % LPP) * CPL;                  // first channel of this lane
+  const int gl = lane % LPP;                          // lane within the pixel's group
+  const int c0 = gl * CPL;                            // first channel of this lane
+  uint4* stage = stage_all + (threadIdx.x >> 5) * kStage + sub * SB;
   const int C = g.C, J = g.J;
   const bool lane_has_channels = c0 < C;              // C % 4 == 0 and CPL % 4 == 0: a lane's float4s are all in or all out
   const int P = g.B * g.H * g.W;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int taps = g.Kh * g.Kw;
+  const float* wlane = wt + c0;
   for (int pw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; pw * PPW < P; pw += warps) {
     const int p = pw * PPW + sub;
     const bool pix_ok = p < P;
@@ -107,12 +122,14 @@ snn_dx_sparse_kernel(const Geometry g, const float* __restrict__ x, const float*
       ph = t % g.H;
       pb = t / g.H;
     }
-    for (int tap = 0; tap < taps; ++tap) {
-      const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
-      // the receptive field that reads this pixel through tap (kh, kw), if there is one
-      int n = 0;
-      const uint4* ents = list;
-      if (pix_ok) {
+    // cursor of this pixel through its lists: tap, and the first entry of that tap's list not staged yet
+    int tap = pix_ok ? 0 : taps, e0 = 0;
+    for (;;) {
+      // ---- stage up to SB entries of this pixel, tap after tap (the terms keep their order: tap-major, j ascending)
+      int staged = 0;
+      while (tap < taps && staged < SB) {
+        const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
+        // the receptive field that reads this pixel through tap (kh, kw), if there is one
         const int hh = ph + g.pad_top - kh, ww = pwid + g.pad_left - kw;
         int nh = hh, nw = ww;
         bool ok = hh >= 0 && ww >= 0;
@@ -121,31 +138,41 @@ snn_dx_sparse_kernel(const Geometry g, const float* __restrict__ x, const float*
           ok = ok && nh * g.Sh == hh && nw * g.Sw == ww;
         }
         ok = ok && nh < g.Nh && nw < g.Nw;
+        int n = 0;
+        const uint4* src = list;
         if (ok) {
           const int r = (pb * g.Nh + nh) * g.Nw + nw;
           n = __ldg(count + r);
-          ents = list + (size_t)r * J;
+          src = list + (size_t)r * J;
         }
+        const int take = min(n - e0, SB - staged);
+        const unsigned tapoff = (unsigned)tap * (unsigned)J;
+        for (int e = gl; e < take; e += LPP) {
+          uint4 en = __ldg(src + e0 + e);
+          en.z = (tapoff + en.z) * (unsigned)C;
+          stage[staged + e] = en;
+        }
+        staged += take;
+        e0 += take;
+        if (e0 >= n) { ++tap; e0 = 0; }
       }
-      const int nmax = __reduce_max_sync(0xffffffffu, n);
-      const float* wtap = wt + (size_t)tap * J * C + c0;
-      // UN entries at a time: their list reads, then their weight reads, then the arithmetic, so that several
-      // loads are in flight per lane. A slot past the end of this pixel's list holds (y = -inf, u = 0, j = 0): its
-      // compare is false for every input and its weight read stays inside the table.
-      constexpr int UN = CPL <= 4 ? 4 : 2;
-      const bool active = lane_has_channels;
+      __syncwarp();
+      const int nmax = __reduce_max_sync(0xffffffffu, staged);
+      if (nmax == 0) break;   // every pixel of the warp is through its lists
+      // ---- the arithmetic over the staged entries. A slot past the end of this pixel's share holds
+      // (y = -inf, u = 0, offset 0): its compare is false for every input and its weight read stays inside the table.
       for (int e = 0; e < nmax; e += UN) {
         uint4 en[UN];
 #pragma unroll
         for (int q = 0; q < UN; ++q) {
           en[q] = make_uint4(0xff800000u, 0u, 0u, 0u);
-          if (e + q < n) en[q] = __ldg(ents + e + q);
+          if (e + q < staged) en[q] = stage[e + q];
         }
-        if (active) {
+        if (lane_has_channels) {
           float4 w4[UN][CPL / 4];
 #pragma unroll
           for (int q = 0; q < UN; ++q) {
-            const float* wrow = wtap + (size_t)en[q].z * C;
+            const float* wrow = wlane + en[q].z;
 #pragma unroll
             for (int k4 = 0; k4 < CPL; k4 += 4)
               w4[q][k4 / 4] = (c0 + k4 < C) ? __ldg(reinterpret_cast<const float4*>(wrow + k4)) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -163,6 +190,7 @@ snn_dx_sparse_kernel(const Geometry g, const float* __restrict__ x, const float*
           }
         }
       }
+      __syncwarp();   // the buffer is rewritten by the next round
     }
     if (pix_ok && lane_has_channels) {
 #pragma unroll

@@ -184,6 +184,26 @@ def test_conv_dx_kernels_agree(case):
     assert torch.equal(a, b)
 
 
+def test_small_fan_in_dw_kernel_matches_the_tile_kernel():
+    """A first layer on three channels has 28 weight rows: its dW runs in the kernel for small fan-in (one lane per
+    weight row) when there are enough receptive fields, and in the register-tile kernel when forced."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    case = [c for c in CONV_CASES if c[0] == 52][0]
+    seed, B, H, W, C, Kh, Kw, Sh, Sw, Kc, bv, padding, dist = case
+    x, w, params, xd, wd, out, outc, (pt, pl, Nh, Nw) = _run_conv(*case)
+    g = np.random.default_rng(seed + 4000).standard_normal((B, Nh, Nw, Kc)).astype(np.float32)
+    g[np.random.default_rng(seed + 2).random(g.shape) < 0.6] = 0
+    gd = torch.from_numpy(g).cuda()
+    _, dw_small, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, need_input_grad=False)
+    _, dw_tile, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, need_input_grad=False, opts=_lib.options(dw_kernel=1))
+    ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64", want_dx=False)
+    P.check_close(dw_small.cpu().numpy(), ref["dw"], "small fan-in dW", abs_sum=ref["dw_abs"])
+    P.check_close(dw_tile.cpu().numpy(), ref["dw"], "tile dW", abs_sum=ref["dw_abs"])
+    _, again, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, need_input_grad=False)
+    assert torch.equal(again, dw_small)
+
+
 def test_conv_inputs_that_never_spike_or_are_not_numbers():
     """Whole pixels, whole channels and single inputs at MAX: empty pixel runs, empty row runs and empty lists."""
     import torch
