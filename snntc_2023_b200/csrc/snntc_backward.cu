@@ -638,9 +638,10 @@ snn_dw_kernel(const Geometry g, const float* __restrict__ uv, const float* __res
 // ------------------------------------------------------------------------------------------- dW, small fan-in
 // At most 32 weight rows (the first convolution of an image network: 3x3x3 + bias = 28): the 128-row tile of
 // snn_dw_kernel would be three quarters padding. Here lane i of every warp owns weight row i and warp w the JB
-// outputs w*JB .. w*JB+JB-1 (J = 8*JB), accumulators in registers; a CTA walks a slice of the rows r. Whether output
-// (r,j) carries a gradient is the same question for all lanes, so rows without one are skipped by a warp-uniform
-// branch. Same arithmetic per element as the other dW kernels (saturating FMA of the scaled difference, FMA with
+// outputs w*JB .. w*JB+JB-1 (J = 8*JB), accumulators in registers; a CTA walks a slice of the rows r, a stage of
+// 4096/J rows at a time through shared memory (u and y tiles copied whole, the inputs gathered a warp per row).
+// Whether output (r,j) carries a gradient is the same question for all lanes, so rows without one are skipped by
+// a warp-uniform branch. Same arithmetic per element as the other dW kernels (saturating FMA of the scaled difference, FMA with
 // -u/s), same exactness rule.
 __device__ __forceinline__ float fma_sat(float a, float b, float c) {
   float r;
@@ -653,13 +654,19 @@ __global__ void __launch_bounds__(kBwdThreads)
 snn_dw_small_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
                     const float* __restrict__ out, float* __restrict__ partial, int rows_per_split,
                     float scale, const int* __restrict__ exact_flag) {
-  const int J = g.J, I = g.I, R = g.R;
+  constexpr int JJ = 8 * JB;              // fan-out
+  constexpr int RS = 4096 / JJ < 64 ? 4096 / JJ : 64;   // rows r per stage: the u and y tiles are at most 16 KB each
+  __shared__ __align__(16) float Us[RS * JJ];
+  __shared__ __align__(16) float Ys[RS * JJ];
+  __shared__ float Xs[RS * 32];
+  __shared__ int4 rowinfo[RS];            // .x element offset of the row's top-left pixel, .y its h, .z its w, .w row valid
+  const int I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
   const bool fast = scale != 1.0f && __ldg(exact_flag) == 0;
   const float sc = fast ? scale : 1.0f;
   const float nsc = -sc;
   const float nusc = fast ? -1.0f / scale : -1.0f;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int j0 = warp * JB;
   const int r_begin = blockIdx.z * rows_per_split;
   const int r_end = min(R, r_begin + rows_per_split);
@@ -675,49 +682,86 @@ snn_dw_small_kernel(const Geometry g, const float* __restrict__ uv, const float*
 #pragma unroll
   for (int q = 0; q < JB; ++q) acc[q] = 0.f;
 
-  for (int r = r_begin; r < r_end; ++r) {
-    float4 u4[JB / 4];
-    const float4* up = reinterpret_cast<const float4*>(uv + (size_t)r * J + j0);
-    bool any = false;
+  for (int rb = r_begin; rb < r_end; rb += RS) {
+    // ---- tiles of this stage: u and y are RS whole rows, contiguous in memory; x is gathered
+    const float4* u4g = reinterpret_cast<const float4*>(uv + (size_t)rb * JJ);
+    const float4* y4g = reinterpret_cast<const float4*>(out + (size_t)rb * JJ);
+    const int valid4 = min(RS, r_end - rb) * (JJ / 4);   // 16-byte chunks that belong to rows of this slice
 #pragma unroll
-    for (int q = 0; q < JB / 4; ++q) {
-      u4[q] = __ldg(up + q);
-      any |= (u4[q].x != 0.f) | (u4[q].y != 0.f) | (u4[q].z != 0.f) | (u4[q].w != 0.f);
+    for (int n = 0; n < (RS * JJ / 4) / kBwdThreads; ++n) {
+      const int e = tid + kBwdThreads * n;
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f), y = u;
+      if (e < valid4) { u = __ldg(u4g + e); y = __ldg(y4g + e); }
+      reinterpret_cast<float4*>(Us)[e] = u;
+      reinterpret_cast<float4*>(Ys)[e] = y;
     }
-    if (!any) continue;   // warp-uniform: every lane read the same values
-    float xv = g.maxv;    // a lane without an input, or a tap outside the image: never spikes
-    if (lane == I && g.has_bias) {
-      xv = g.biasvolt;
-    } else if (lane < I) {
-      if (!g.is_conv) {
-        xv = __ldg(x + (size_t)r * I + lane);
-      } else {
+    if (g.is_conv && tid < RS) {
+      const int r = rb + tid;
+      int4 ri = make_int4(0, 0, 0, 0);
+      if (r < r_end) {
         const int nw = r % g.Nw;
         const int t = r / g.Nw;
         const int nh = t % g.Nh;
         const int b = t / g.Nh;
-        const int h0 = nh * g.Sh - g.pad_top, w0 = nw * g.Sw - g.pad_left;
-        if ((unsigned)(h0 + l_kh) < (unsigned)g.H && (unsigned)(w0 + l_kw) < (unsigned)g.W)
-          xv = __ldg(x + ((ptrdiff_t)(b * g.H + h0) * g.W + w0) * g.C + l_off);
+        ri.y = nh * g.Sh - g.pad_top;
+        ri.z = nw * g.Sw - g.pad_left;
+        ri.x = ((b * g.H + ri.y) * g.W + ri.z) * g.C;
+        ri.w = 1;
+      }
+      rowinfo[tid] = ri;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < (RS * 32) / kBwdThreads; ++n) {
+      const int rl = warp + (kBwdThreads / 32) * n;    // a warp per row, lane = weight row
+      const int r = rb + rl;
+      float xv = g.maxv;    // a lane without an input, a row past the slice, a tap outside the image: never spikes
+      if (r < r_end) {
+        if (lane == I && g.has_bias) {
+          xv = g.biasvolt;
+        } else if (lane < I) {
+          if (!g.is_conv) {
+            xv = __ldg(x + (size_t)r * I + lane);
+          } else {
+            const int4 ri = rowinfo[rl];
+            if ((unsigned)(ri.y + l_kh) < (unsigned)g.H && (unsigned)(ri.z + l_kw) < (unsigned)g.W)
+              xv = __ldg(x + (ptrdiff_t)ri.x + l_off);
+          }
+        }
+      }
+      Xs[rl * 32 + lane] = xv;
+    }
+    __syncthreads();
+    // ---- this warp's JB outputs against all rows of the stage
+#pragma unroll 2
+    for (int rl = 0; rl < RS; ++rl) {
+      float4 u4[JB / 4];
+      bool any = false;
+#pragma unroll
+      for (int q = 0; q < JB / 4; ++q) {
+        u4[q] = *reinterpret_cast<const float4*>(Us + rl * JJ + j0 + 4 * q);
+        any |= (u4[q].x != 0.f) | (u4[q].y != 0.f) | (u4[q].z != 0.f) | (u4[q].w != 0.f);
+      }
+      if (!any) continue;   // warp-uniform: every lane read the same values
+      const float xv = Xs[rl * 32 + lane];
+#pragma unroll
+      for (int q = 0; q < JB / 4; ++q) {
+        const float uu[4] = {u4[q].x, u4[q].y, u4[q].z, u4[q].w};
+        if (uu[0] == 0.f && uu[1] == 0.f && uu[2] == 0.f && uu[3] == 0.f) continue;
+        const float4 y4 = *reinterpret_cast<const float4*>(Ys + rl * JJ + j0 + 4 * q);
+        const float yy[4] = {y4.x, y4.y, y4.z, y4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          // (a zero u adds +-0: no need to branch inside a group of four)
+          const float t = fast ? fma_sat(xv, nsc, yy[k] * sc) : fmaxf(yy[k] - xv, 0.f);
+          acc[4 * q + k] = fmaf(t, uu[k] * nusc, acc[4 * q + k]);
+        }
       }
     }
-    const float4* yp = reinterpret_cast<const float4*>(out + (size_t)r * J + j0);
-#pragma unroll
-    for (int q = 0; q < JB / 4; ++q) {
-      const float uu[4] = {u4[q].x, u4[q].y, u4[q].z, u4[q].w};
-      if (uu[0] == 0.f && uu[1] == 0.f && uu[2] == 0.f && uu[3] == 0.f) continue;
-      const float4 y4 = __ldg(yp + q);
-      const float yy[4] = {y4.x, y4.y, y4.z, y4.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        // (a zero u adds +-0: no need to branch inside a group of four)
-        const float t = fast ? fma_sat(xv, nsc, yy[k] * sc) : fmaxf(yy[k] - xv, 0.f);
-        acc[4 * q + k] = fmaf(t, uu[k] * nusc, acc[4 * q + k]);
-      }
-    }
+    __syncthreads();   // the tiles are overwritten by the next stage
   }
   if (lane < Itot) {
-    float* dst = partial + (size_t)blockIdx.z * Itot * J + (size_t)lane * J + j0;
+    float* dst = partial + (size_t)blockIdx.z * Itot * JJ + (size_t)lane * JJ + j0;
 #pragma unroll
     for (int q = 0; q < JB; ++q) dst[q] = acc[q];
   }

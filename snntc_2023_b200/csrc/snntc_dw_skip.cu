@@ -66,9 +66,7 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
   float* Xs = reinterpret_cast<float*>(smem_raw);                 // [2][kRS][kTI]
   float* Ys = Xs + 2 * kRS * kTI;                                 // [2][kRS][kJT]
   float* Us = Ys + 2 * kRS * kJT;                                 // [2][kRS][kJT]
-  int4* tapinfo = reinterpret_cast<int4*>(Us + 2 * kRS * kJT);    // [kCh]: .x element offset from the row's top-left pixel,
-                                                                  //        .y kh, .z kw, .w 1 = image tap, 2 = bias chunk, 0 = padding
-  int4* rowinfo = tapinfo + kCh;                                  // [2][kRS]: .x element offset of the top-left pixel, .y its h, .z its w, .w row valid
+  int4* rowinfo = reinterpret_cast<int4*>(Us + 2 * kRS * kJT);    // [2][kRS]: .x element offset of the top-left pixel, .y its h, .z its w, .w row valid
 
   const int J = g.J, I = g.I, R = g.R;
   const int Itot = I + g.has_bias;
@@ -85,17 +83,18 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
   const float4 v_never = make_float4(g.maxv, g.maxv, g.maxv, g.maxv);
   const float4 v_bias = make_float4(g.biasvolt, g.maxv, g.maxv, g.maxv);
 
-  for (int q = tid; q < kCh; q += kThreads) {
-    const int i = i0 + 4 * q;
-    int4 t = make_int4(0, 0, 0, 0);
+  // this thread's column chunk of the x tile (threads below kCh): .x element offset of its tap from a row's top-left
+  // pixel, .y kh, .z kw, .w 1 = image tap, 2 = bias chunk, 0 = padding behind the last weight row
+  int4 tapinfo_reg = make_int4(0, 0, 0, 0);
+  if (tid < kCh) {
+    const int i = i0 + 4 * tid;
     if (i < I) {
       const int tap = i / g.C, c = i - tap * g.C;
       const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
-      t = make_int4((kh * g.W + kw) * g.C + c, kh, kw, 1);
+      tapinfo_reg = make_int4((kh * g.W + kw) * g.C + c, kh, kw, 1);
     } else if (i == I && g.has_bias) {
-      t.w = 2;
+      tapinfo_reg.w = 2;
     }
-    tapinfo[q] = t;
   }
   auto fill_rowinfo = [&](int buf, int rb) {
     if (tid < kRS) {
@@ -114,30 +113,33 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
       rowinfo[buf * kRS + tid] = ri;
     }
   };
-  // queues the asynchronous copies of the 16 rows starting at rb into buffer `buf` (rowinfo[buf] describes them)
+  // Queues the asynchronous copies of the 16 rows starting at rb into buffer `buf` (rowinfo[buf] describes them).
+  // Thread t < kCh owns column chunk t of the x tile -- its tap is the same for every row and stays in registers --
+  // and walks the 16 rows; the other threads fetch the y and u tiles (16 rows x 8 chunks each).
+  static_assert(kCh < kThreads, "some threads must be left for the y and u tiles");
+  const int4 my_tap = tapinfo_reg;
   auto issue = [&](int buf, int rb) {
-    float* xs = Xs + buf * kRS * kTI;
+    if (tid < kCh) {
+      float* dst = Xs + buf * kRS * kTI + 4 * tid;
 #pragma unroll
-    for (int n = 0; n < (kRS * kCh) / kThreads; ++n) {
-      const int e = tid + kThreads * n;
-      const int rl = e / kCh, q = e - rl * kCh;
-      const int4 ri = rowinfo[buf * kRS + rl];
-      const int4 ti = tapinfo[q];
-      float* dst = xs + rl * kTI + 4 * q;
-      const bool in_image = ri.w != 0 && ti.w == 1 && (unsigned)(ri.y + ti.y) < (unsigned)g.H &&
-                            (unsigned)(ri.z + ti.z) < (unsigned)g.W;
-      if (in_image) cp_async16(dst, x + ((ptrdiff_t)ri.x + ti.x));
-      else *reinterpret_cast<float4*>(dst) = (ri.w != 0 && ti.w == 2) ? v_bias : v_never;
-    }
-    {
-      // y and u: 16 rows x 8 chunks each; threads 0..127 fetch y, 128..255 u
-      const int h = tid & 127;
-      const int rl = h >> 3, cq = h & 7;
-      const int r = rb + rl, j = j0 + 4 * cq;
-      const float* base = (tid < 128) ? out : uv;
-      float* dst = ((tid < 128) ? Ys : Us) + (buf * kRS + rl) * kJT + 4 * cq;
-      if (r < r_end && j < J) cp_async16(dst, base + (size_t)r * J + j);
-      else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);   // no spike value, no gradient
+      for (int rl = 0; rl < kRS; ++rl) {
+        const int4 ri = rowinfo[buf * kRS + rl];   // the same word for the whole warp: a broadcast
+        const bool in_image = ri.w != 0 && my_tap.w == 1 && (unsigned)(ri.y + my_tap.y) < (unsigned)g.H &&
+                              (unsigned)(ri.z + my_tap.z) < (unsigned)g.W;
+        if (in_image) cp_async16(dst + rl * kTI, x + ((ptrdiff_t)ri.x + my_tap.x));
+        else *reinterpret_cast<float4*>(dst + rl * kTI) = (ri.w != 0 && my_tap.w == 2) ? v_bias : v_never;
+      }
+    } else {
+      for (int e = tid - kCh; e < 2 * kRS * (kJT / 4); e += kThreads - kCh) {
+        const int which = e / (kRS * (kJT / 4));            // 0: y, 1: u
+        const int h = e - which * (kRS * (kJT / 4));
+        const int rl = h / (kJT / 4), cq = h - rl * (kJT / 4);
+        const int r = rb + rl, j = j0 + 4 * cq;
+        const float* base = which == 0 ? out : uv;
+        float* dst = (which == 0 ? Ys : Us) + (buf * kRS + rl) * kJT + 4 * cq;
+        if (r < r_end && j < J) cp_async16(dst, base + (size_t)r * J + j);
+        else *reinterpret_cast<float4*>(dst) = make_float4(0.f, 0.f, 0.f, 0.f);   // no spike value, no gradient
+      }
     }
     cp_async_commit();
   };
@@ -152,12 +154,18 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
   auto reduce_stage = [&](int buf, auto fast_c) {
     constexpr bool FAST = decltype(fast_c)::value;
     const float* xs = Xs + buf * kRS * kTI;
+    // which of the 16 rows carry a gradient for one of this warp's four channels: lane rl looks at row rl, one vote
+    unsigned todo;
+    {
+      const float4 uq = *reinterpret_cast<const float4*>(Us + (buf * kRS + (lane & (kRS - 1))) * kJT + 4 * warp);
+      todo = __ballot_sync(0xffffffffu, (uq.x != 0.f) | (uq.y != 0.f) | (uq.z != 0.f) | (uq.w != 0.f)) & ((1u << kRS) - 1u);
+    }
 #pragma unroll 1
-    for (int rl = 0; rl < kRS; ++rl) {
+    while (todo != 0u) {
+      const int rl = __ffs((int)todo) - 1;
+      todo &= todo - 1u;
       const float4 y4 = *reinterpret_cast<const float4*>(Ys + (buf * kRS + rl) * kJT + 4 * warp);
       const float4 u4 = *reinterpret_cast<const float4*>(Us + (buf * kRS + rl) * kJT + 4 * warp);
-      // warp-uniform: the four values are the same in every lane
-      if (u4.x == 0.f && u4.y == 0.f && u4.z == 0.f && u4.w == 0.f) continue;
       float xr[QL][4];
 #pragma unroll
       for (int c = 0; c < QL; ++c) {
@@ -224,8 +232,8 @@ snn_dw_skip_kernel(const Geometry g, const float* __restrict__ uv, const float* 
 }
 
 size_t smem_bytes(int QL) {
-  const size_t kTI = 128 * (size_t)QL, kCh = 32 * (size_t)QL;
-  return (2 * kRS * kTI + 4 * kRS * kJT) * sizeof(float) + (kCh + 2 * kRS) * sizeof(int4);
+  const size_t kTI = 128 * (size_t)QL;
+  return (2 * kRS * kTI + 4 * kRS * kJT) * sizeof(float) + 2 * kRS * sizeof(int4);
 }
 
 // fan-in tiles: as few as possible with at most 640 rows each, then the narrowest tile that covers the share
