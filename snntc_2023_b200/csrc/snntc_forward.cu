@@ -1015,7 +1015,7 @@ int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g
 // Lists of a conv layer are built by per-pixel sorting and merging when the geometry allows it and the row
 // sort would sort every input pixel several times over (3x3 stride 1: nine times).
 bool use_merge_lists(const Geometry& g, const Options& opt) {
-  if (opt.list_builder == 1 || !merge_lists_supported(g)) return false;
+  if ((opt.list_builder & 3) == 1 || !merge_lists_supported(g)) return false;
   return true;
 }
 
@@ -1077,7 +1077,11 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
-    if (variant == 1) return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+    if (variant == 1) {
+      // pairs layout: 64 outputs per warp, or (walk_outputs 3) 128 as two pairs per lane
+      if (jsel >= 2) return launch_walk2<2>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+      return launch_walk2<1>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
+    }
     if (jsel == 0) return launch_walk<1, false>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
     if (variant == 3) {
       if (jsel == 1) return launch_walk<2, true>(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage);
@@ -1090,7 +1094,7 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
 
   if (use_merge_lists(g, opt)) {
     if (fparts & 1) {
-      const int rc = launch_merge_lists(g, x, keys_g, nvalid_g, istride, merge_scratch, li, s);
+      const int rc = launch_merge_lists(g, x, keys_g, nvalid_g, istride, merge_scratch, (opt.list_builder >> 2) - 1, li, s);
       if (rc != OK) return rc;
     }
     return walk(s, 0, g.R);

@@ -10,6 +10,8 @@
 //                   (h, nw - pad_left + kw) -- shared by the Kh receptive fields that contain that row segment;
 //   3. field lists  one thread per receptive field: sequential merge of its Kh row runs, written in the format
 //                   the walk kernels read: (x, element offset of weight row ((kh*Kw+kw)*C+c)).
+// Where a layer has too few row segments or fields to fill the GPU with one thread each (deep layers: small
+// images, many channels), 2 to 16 neighbouring threads share a merge, cut into pieces by value.
 // A sequential two- or three-way merge costs a few dozen instructions per entry and thread and needs no
 // cooperation between threads; the per-field radix sort it replaces spends about five hundred per entry.
 // Each thread streams through its own runs, so what bounds these kernels is the number of memory transactions:
@@ -126,67 +128,110 @@ struct BlockedMem {
                  :: "l"(dst), "r"(e[0].x), "r"(e[0].y), "r"(e[1].x), "r"(e[1].y), "r"(e[2].x), "r"(e[2].y), "r"(e[3].x), "r"(e[3].y)
                  : "memory");
   }
+  __device__ __forceinline__ void store1(WalkEntry* dst, const WalkEntry& e) const { *dst = e; }
 };
 
-// One thread per (b, h, nw): merge of the pixel runs (b, h, nw - pad_left + kw), kw < Kw, columns outside the
-// image being empty. Entry offsets gain kw*C*J.
+// One piece of a merge that `parts` neighbouring lanes share (parts a power of two up to 32, so the lanes of one
+// merge sit in one warp): every lane finds its own cut by binary search, takes the next lane's as its end and
+// merges what lies between. All 32 lanes of the warp must call this, n[] being zero for lanes without work.
+__device__ __forceinline__ void merge_piece(const WalkEntry* const* run, const int* n, const uint32_t* off, int part,
+                                            int parts, WalkEntry* dst, BlockedMem& mem) {
+  int cut[3], end[3];
+  merge3_cut<WalkEntry>(run, n, part, parts, cut);
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    end[k] = __shfl_down_sync(0xffffffffu, cut[k], 1);
+    if (part == parts - 1) end[k] = n[k];
+  }
+  const int count = (end[0] - cut[0]) + (end[1] - cut[1]) + (end[2] - cut[2]);
+  merge3_runs_blocked_range<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], cut[0], cut[1],
+                                                   cut[2], count, dst, mem);
+}
+
+// One thread (SPLIT: `parts` neighbouring threads, each a piece) per (b, h, nw): merge of the pixel runs
+// (b, h, nw - pad_left + kw), kw < Kw, columns outside the image being empty. Entry offsets gain kw*C*J.
+template <bool SPLIT>
 __global__ void __launch_bounds__(kListThreads)
 snn_row_runs_kernel(const Geometry g, const WalkEntry* __restrict__ pix, const int* __restrict__ pix_n, int pix_stride,
-                    WalkEntry* __restrict__ rows, int* __restrict__ rows_n, int row_stride) {
+                    WalkEntry* __restrict__ rows, int* __restrict__ rows_n, int row_stride, int parts_log2) {
   __shared__ uint2 windows[3 * 4 * kListThreads];
   BlockedMem mem = {windows + threadIdx.x};
-  const int total_threads = g.B * g.H * g.Nw;
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= total_threads) return;
+  const int items = g.B * g.H * g.Nw;
+  const int thread = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t = SPLIT ? (thread >> parts_log2) : thread;
+  const bool valid = t < items;
+  if (!SPLIT && !valid) return;
   const int nw = t % g.Nw;
   const int bh = t / g.Nw;                            // b*H + h
   const WalkEntry* run[3] = {g_empty_run, g_empty_run, g_empty_run};
   uint32_t off[3] = {0u, 0u, 0u};
-  int total = 0;
+  int n[3] = {0, 0, 0};
 #pragma unroll
   for (int kw = 0; kw < 3; ++kw) {
     const int wc = nw - g.pad_left + kw;
-    if (kw < g.Kw && wc >= 0 && wc < g.W) {
+    if (valid && kw < g.Kw && wc >= 0 && wc < g.W) {
       const int p = bh * g.W + wc;
       run[kw] = pix + (size_t)p * pix_stride;
-      total += __ldg(pix_n + p);
+      n[kw] = __ldg(pix_n + p);
     }
     off[kw] = (uint32_t)kw * (uint32_t)g.C * (uint32_t)g.J;
   }
-  merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total,
-                                             rows + (size_t)t * row_stride, true, mem);
-  rows_n[t] = total;
+  const int total = n[0] + n[1] + n[2];
+  WalkEntry* dst = rows + (size_t)(valid ? t : 0) * row_stride;
+  if (SPLIT) {
+    const int part = thread & ((1 << parts_log2) - 1);
+    merge_piece(run, n, off, part, 1 << parts_log2, dst, mem);
+    if (valid && part == 0) {
+      dst[total] = make_uint2(kRunEndBits, 0u);
+      rows_n[t] = total;
+    }
+  } else {
+    merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total, dst, true, mem);
+    rows_n[t] = total;
+  }
 }
 
-// One thread per receptive field r = (b*Nh + nh)*Nw + nw: merge of the row runs (b, nh - pad_top + kh, nw),
-// kh < Kh, rows outside the image being empty. Entry offsets gain kh*Kw*C*J.
+// One thread (SPLIT: `parts` neighbouring threads, each a piece) per receptive field r = (b*Nh + nh)*Nw + nw:
+// merge of the row runs (b, nh - pad_top + kh, nw), kh < Kh, rows outside the image being empty. Entry offsets
+// gain kh*Kw*C*J.
+template <bool SPLIT>
 __global__ void __launch_bounds__(kListThreads)
 snn_field_lists_kernel(const Geometry g, const WalkEntry* __restrict__ rows, const int* __restrict__ rows_n,
-                       int row_stride, WalkEntry* __restrict__ lists, int* __restrict__ nvalid, int istride) {
+                       int row_stride, WalkEntry* __restrict__ lists, int* __restrict__ nvalid, int istride,
+                       int parts_log2) {
   __shared__ uint2 windows[3 * 4 * kListThreads];
   BlockedMem mem = {windows + threadIdx.x};
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= g.R) return;
+  const int thread = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = SPLIT ? (thread >> parts_log2) : thread;
+  const bool valid = r < g.R;
+  if (!SPLIT && !valid) return;
   const int nw = r % g.Nw;
   const int t0 = r / g.Nw;
   const int nh = t0 % g.Nh;
   const int b = t0 / g.Nh;
   const WalkEntry* run[3] = {g_empty_run, g_empty_run, g_empty_run};
   uint32_t off[3] = {0u, 0u, 0u};
-  int total = 0;
+  int n[3] = {0, 0, 0};
 #pragma unroll
   for (int kh = 0; kh < 3; ++kh) {
     const int h = nh - g.pad_top + kh;
-    if (kh < g.Kh && h >= 0 && h < g.H) {
+    if (valid && kh < g.Kh && h >= 0 && h < g.H) {
       const int t = (b * g.H + h) * g.Nw + nw;
       run[kh] = rows + (size_t)t * row_stride;
-      total += __ldg(rows_n + t);
+      n[kh] = __ldg(rows_n + t);
     }
     off[kh] = (uint32_t)kh * (uint32_t)g.Kw * (uint32_t)g.C * (uint32_t)g.J;
   }
-  merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total,
-                                             lists + (size_t)r * istride, false, mem);
-  nvalid[r] = total;
+  const int total = n[0] + n[1] + n[2];
+  WalkEntry* dst = lists + (size_t)(valid ? r : 0) * istride;
+  if (SPLIT) {
+    const int part = thread & ((1 << parts_log2) - 1);
+    merge_piece(run, n, off, part, 1 << parts_log2, dst, mem);
+    if (valid && part == 0) nvalid[r] = total;
+  } else {
+    merge3_runs_blocked<WalkEntry, BlockedMem>(run[0], run[1], run[2], off[0], off[1], off[2], total, dst, false, mem);
+    nvalid[r] = total;
+  }
 }
 
 // entries per pixel run and per row run: room for the terminator, rounded up to four entries (32 bytes)
@@ -224,8 +269,18 @@ bool merge_lists_shape_ok(const Geometry& g) {
 
 size_t merge_lists_bytes(const Geometry& g) { return merge_scratch(g).total; }
 
+// pieces per merge (as a power of two): enough that the merge kernels have about 768 threads per SM to run, and
+// two pieces where one per merge would leave the last quarter of the thread slots empty (measured: 12.5 k to 65 k
+// merges are fastest with about 100 k to 130 k threads, 200 k merges in two pieces, 262 k in one)
+int merge_split_log2(int items, const LaunchInfo& li) {
+  int lg = 0;
+  while (lg < 4 && ((long)items << lg) < (long)li.num_sms * 768) ++lg;
+  if (lg == 0 && items < li.num_sms * 1536) lg = 1;
+  return lg;
+}
+
 int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
-                       void* scratch, const LaunchInfo& li, cudaStream_t s) {
+                       void* scratch, int split_log2, const LaunchInfo& li, cudaStream_t s) {
   const MergeScratch m = merge_scratch(g);
   unsigned char* base = static_cast<unsigned char*>(scratch);
   WalkEntry* pix = reinterpret_cast<WalkEntry*>(base + m.pix);
@@ -249,11 +304,21 @@ int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int*
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
 
   const int nrow = g.B * g.H * g.Nw;
-  snn_row_runs_kernel<<<(nrow + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, pix, pix_n, ps, rows, rows_n, rs);
+  int lg = split_log2 >= 0 ? (split_log2 > 5 ? 5 : split_log2) : merge_split_log2(nrow, li);
+  if (((long)nrow << lg) > 0x7fffffffL - kListThreads) lg = 0;
+  if (lg == 0)
+    snn_row_runs_kernel<false><<<(nrow + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, pix, pix_n, ps, rows, rows_n, rs, 0);
+  else
+    snn_row_runs_kernel<true><<<(int)((((long)nrow << lg) + kListThreads - 1) / kListThreads), kListThreads, 0, s>>>(g, pix, pix_n, ps, rows, rows_n, rs, lg);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
 
-  snn_field_lists_kernel<<<(g.R + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride);
+  lg = split_log2 >= 0 ? (split_log2 > 5 ? 5 : split_log2) : merge_split_log2(g.R, li);
+  if (((long)g.R << lg) > 0x7fffffffL - kListThreads) lg = 0;
+  if (lg == 0)
+    snn_field_lists_kernel<false><<<(g.R + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride, 0);
+  else
+    snn_field_lists_kernel<true><<<(int)((((long)g.R << lg) + kListThreads - 1) / kListThreads), kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride, lg);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }

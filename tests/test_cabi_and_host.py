@@ -174,7 +174,23 @@ struct HostMem {
   void load_window(int run, const uint2* src) { memcpy(w[run], src, sizeof(w[run])); }
   uint2 window(int run, int k) const { return w[run][k]; }
   void store4(uint2* dst, const uint2 (&e)[4]) const { memcpy(dst, e, sizeof(e)); }
+  void store1(uint2* dst, const uint2& e) const { *dst = e; }
 };
+// the merge cut into `parts` pieces by value, the pieces run one after the other in reverse order
+extern "C" void merge3_split(const uint2* a, const uint2* b, const uint2* c, int na, int nb, int nc, unsigned oa,
+                             unsigned ob, unsigned oc, uint2* dst, int parts, int* piece_sizes) {
+  const uint2* run[3] = {a, b, c};
+  const int n[3] = {na, nb, nc};
+  for (int part = parts - 1; part >= 0; --part) {
+    int cut[3], end[3];
+    snntc::merge3_cut<uint2>(run, n, part, parts, cut);
+    snntc::merge3_cut<uint2>(run, n, part + 1, parts, end);
+    const int count = end[0] - cut[0] + end[1] - cut[1] + end[2] - cut[2];
+    piece_sizes[part] = count;
+    HostMem mem;
+    snntc::merge3_runs_blocked_range<uint2, HostMem>(a, b, c, oa, ob, oc, cut[0], cut[1], cut[2], count, dst, mem);
+  }
+}
 extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned oa, unsigned ob, unsigned oc,
                        int total, uint2* dst, int terminate, int blocked) {
   if (blocked) {
@@ -223,3 +239,12 @@ extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned 
                 assert dst[total + 1, 0] == 0xDEADBEEF
             else:   # whole groups of four are written, nothing behind the last group
                 assert np.all(dst[(total + 3) // 4 * 4 + (1 if (trial % 3 == 0 and total % 4 == 0) else 0):, 0] == 0xDEADBEEF)
+            # the same merge cut into pieces by value: same entries in the same places, nothing written behind them
+            for parts in (2, 8, 32):
+                dst2 = np.full_like(dst, 0xDEADBEEF)
+                sizes = np.zeros(parts, np.int32)
+                lib.merge3_split(ptr(runs[0]), ptr(runs[1]), ptr(runs[2]), n[0], n[1], n[2], offs[0], offs[1], offs[2],
+                                 ptr(dst2), parts, sizes.ctypes.data_as(ctypes.c_void_p))
+                assert int(sizes.sum()) == total and sizes.min() >= 0
+                assert np.array_equal(dst2[:total], dst[:total])
+                assert np.all(dst2[total:, 0] == 0xDEADBEEF)

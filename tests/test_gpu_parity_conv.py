@@ -124,6 +124,10 @@ def test_conv_list_builders_agree(case):
     xp = O.pad_like_reference(x, Kh, Kw, Sh, Sw, padding)
     bp = ops.snn_cv(torch.from_numpy(xp).cuda(), wd, params, opts=_lib.options(list_builder=2)).cpu().numpy()
     assert np.array_equal(bp, b)
+    # merges cut into 1, 2, 8 and 32 pieces build the same lists entry for entry
+    for k in (0, 1, 3, 5):
+        c = ops.snn_cv(xd, wd, params, pt, pl, Nh, Nw, opts=_lib.options(list_builder=2 + 4 * (k + 1))).cpu().numpy()
+        assert np.array_equal(c, b), "pieces per merge: %d" % (1 << k)
 
 
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
