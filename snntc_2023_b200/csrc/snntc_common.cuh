@@ -38,7 +38,8 @@ struct Options {
   int walk_layout = 0;      // 0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane;
                             // +4: read list entries straight from global memory instead of through shared memory
   int walk_outputs = 0;     // 0 auto, 1..4: 1, 2, 4, 8 outputs per lane (pairs layout: 2 only)
-  int list_builder = 0;     // 0 auto, 1 per-row radix sort, 2 per-pixel sort + merges (3x3 stride-1 conv only);
+  int list_builder = 0;     // 0 auto, 1 per-row radix sort, 2 per-pixel sort + merges (3x3 stride-1 conv only),
+                            // 3 per-row sorting network in registers (rows of at most 256 inputs);
                             // + 4*(k+1): the merges are cut into 2^k pieces each (k = 0 .. 5) instead of auto
   int backward_parts = 3;   // bit 0: dX, bit 1: dW
   int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0)
@@ -89,6 +90,11 @@ size_t merge_lists_bytes(const Geometry& g);
 // split_log2: pieces per merge as a power of two (0 .. 5), -1 = chosen from the number of merges
 int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
                        void* scratch, int split_log2, const LaunchInfo& li, cudaStream_t s);
+
+// Sorted lists of rows of at most 256 inputs by a sorting network in registers, one warp per row (snntc_lists.cu).
+bool small_rows_supported(const Geometry& g);
+int launch_small_rows(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
+                      const LaunchInfo& li, cudaStream_t s);
 
 // ---- backward --------------------------------------------------------------------------------
 size_t backward_workspace_bytes(const Geometry& g, const LaunchInfo& li);

@@ -1015,7 +1015,15 @@ int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g
 // Lists of a conv layer are built by per-pixel sorting and merging when the geometry allows it and the row
 // sort would sort every input pixel several times over (3x3 stride 1: nine times).
 bool use_merge_lists(const Geometry& g, const Options& opt) {
-  if ((opt.list_builder & 3) == 1 || !merge_lists_supported(g)) return false;
+  const int want = opt.list_builder & 3;
+  if (want == 1 || want == 3 || !merge_lists_supported(g)) return false;
+  return true;
+}
+
+// Short rows (a first layer on a few image channels) are sorted by a network in registers.
+bool use_small_rows(const Geometry& g, const Options& opt) {
+  const int want = opt.list_builder & 3;
+  if (want == 1 || want == 2 || !small_rows_supported(g)) return false;
   return true;
 }
 
@@ -1095,6 +1103,13 @@ int launch_forward(const Geometry& g, const float* x, const float* w, float* out
   if (use_merge_lists(g, opt)) {
     if (fparts & 1) {
       const int rc = launch_merge_lists(g, x, keys_g, nvalid_g, istride, merge_scratch, (opt.list_builder >> 2) - 1, li, s);
+      if (rc != OK) return rc;
+    }
+    return walk(s, 0, g.R);
+  }
+  if (use_small_rows(g, opt)) {
+    if (fparts & 1) {
+      const int rc = launch_small_rows(g, x, keys_g, nvalid_g, istride, li, s);
       if (rc != OK) return rc;
     }
     return walk(s, 0, g.R);

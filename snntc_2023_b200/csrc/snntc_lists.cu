@@ -105,6 +105,79 @@ snn_pixel_runs_kernel(const float* __restrict__ x, int npix, int C, int J, float
   }
 }
 
+// Rows of at most 256 inputs (the first layer of a network: a few channels under a small kernel), one warp per
+// row: the inputs that can spike, gathered tap by tap through a table in shared memory, sorted by the same
+// register network on (value, source index) -- ties in index order, like a stable sort -- and written straight
+// as the list the walk reads. A dense row is its own table.
+template <int EPL>
+__global__ void __launch_bounds__(kPixelWarps * 32)
+snn_small_rows_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* __restrict__ lists,
+                      int* __restrict__ nvalid, int istride) {
+  __shared__ int tap_off[32 * EPL];
+  __shared__ unsigned short tap_khw[32 * EPL];
+  const int I = g.I;
+  if (g.is_conv) {
+    for (int i = threadIdx.x; i < 32 * EPL; i += blockDim.x) {
+      int o = 0;
+      unsigned kk = 0;
+      if (i < I) {
+        const int tap = i / g.C, c = i - tap * g.C;
+        const int kh = tap / g.Kw, kw = tap - kh * g.Kw;
+        o = (kh * g.W + kw) * g.C + c;
+        kk = (unsigned)(kh << 8 | kw);
+      }
+      tap_off[i] = o;
+      tap_khw[i] = (unsigned short)kk;
+    }
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const float maxcomp = g.maxv - 0.1f;
+  for (int r = blockIdx.x * kPixelWarps + warp; r < g.R; r += gridDim.x * kPixelWarps) {
+    const float* xr = x + (size_t)r * I;
+    int h0 = 0, w0 = 0;
+    if (g.is_conv) {
+      const int nw = r % g.Nw;
+      const int t = r / g.Nw;
+      const int nh = t % g.Nh;
+      const int b = t / g.Nh;
+      h0 = nh * g.Sh - g.pad_top;
+      w0 = nw * g.Sw - g.pad_left;
+      // the row's top-left input pixel; may lie outside the image, in which case it is never dereferenced
+      xr = x + ((ptrdiff_t)b * g.H * g.W + (ptrdiff_t)h0 * g.W + w0) * g.C;
+    }
+    u64 v[EPL];
+    int n = 0;
+#pragma unroll
+    for (int m = 0; m < EPL; ++m) {
+      const int i = m * 32 + lane;
+      bool ok = i < I;
+      ptrdiff_t o = i;
+      if (g.is_conv) {
+        const unsigned khw = tap_khw[i];
+        o = tap_off[i];
+        ok = ok && (unsigned)(h0 + (int)(khw >> 8)) < (unsigned)g.H && (unsigned)(w0 + (int)(khw & 255u)) < (unsigned)g.W;
+      }
+      float val = CUDART_INF_F;
+      if (ok) val = __ldg(xr + o);
+      const bool keep = val <= maxcomp;               // false for NaN, padding and inputs that never spike
+      v[m] = keep ? (((u64)float_to_sortable(val) << 32) | (unsigned)i) : ~0ull;
+      n += __popc(__ballot_sync(0xffffffffu, keep));
+    }
+    warp_bitonic_sort<EPL>(v, lane);
+    WalkEntry* dst = lists + (size_t)r * istride;
+#pragma unroll
+    for (int m = 0; m < EPL; ++m) {
+      const int rank = lane * EPL + m;
+      if (rank < n)
+        dst[rank] = make_uint2(__float_as_uint(sortable_to_float((uint32_t)(v[m] >> 32))),
+                               (uint32_t)v[m] * (uint32_t)g.J);
+    }
+    if (lane == 0) nvalid[r] = n;
+  }
+}
+
 __device__ __align__(32) const WalkEntry g_empty_run[4] = {{kRunEndBits, 0u}, {kRunEndBits, 0u}, {kRunEndBits, 0u}, {kRunEndBits, 0u}};
 
 // How merge3_runs_blocked reaches memory on the device: 32-byte global reads and writes (256-bit accesses of
@@ -319,6 +392,26 @@ int launch_merge_lists(const Geometry& g, const float* x, WalkEntry* lists, int*
     snn_field_lists_kernel<false><<<(g.R + kListThreads - 1) / kListThreads, kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride, 0);
   else
     snn_field_lists_kernel<true><<<(int)((((long)g.R << lg) + kListThreads - 1) / kListThreads), kListThreads, 0, s>>>(g, rows, rows_n, rs, lists, nvalid, istride, lg);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
+}
+
+bool small_rows_supported(const Geometry& g) {
+  if (g.I < 1 || g.I > 256) return false;
+  if (g.is_conv && (g.Kh > 255 || g.Kw > 255)) return false;
+  return true;
+}
+
+int launch_small_rows(const Geometry& g, const float* x, WalkEntry* lists, int* nvalid, int istride,
+                      const LaunchInfo& li, cudaStream_t s) {
+  long grid = ((long)g.R + kPixelWarps - 1) / kPixelWarps;
+  const long cap = (long)li.num_sms * 8;
+  if (grid > cap) grid = cap;
+  const int epl = (g.I + 31) / 32;
+  if (epl <= 1) snn_small_rows_kernel<1><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
+  else if (epl <= 2) snn_small_rows_kernel<2><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
+  else if (epl <= 4) snn_small_rows_kernel<4><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
+  else snn_small_rows_kernel<8><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }

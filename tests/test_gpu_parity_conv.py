@@ -130,6 +130,20 @@ def test_conv_list_builders_agree(case):
         assert np.array_equal(c, b), "pieces per merge: %d" % (1 << k)
 
 
+SMALL_ROW_CASES = [c for c in CONV_CASES if c[5] * c[6] * c[4] <= 256]
+
+
+@pytest.mark.parametrize("case", SMALL_ROW_CASES, ids=_ids)
+def test_conv_small_row_builder_matches_the_row_sort(case):
+    """Rows of at most 256 inputs sorted by the register network and by the per-row radix sort: both order equal
+    inputs by source index, so the lists and with them every output bit are the same."""
+    from snntc_2023_b200 import _lib, ops
+    x, w, params, xd, wd, out, outc, (pt, pl, Nh, Nw) = _run_conv(*case)
+    a = ops.snn_cv(xd, wd, params, pt, pl, Nh, Nw, opts=_lib.options(list_builder=1)).cpu().numpy()
+    b = ops.snn_cv(xd, wd, params, pt, pl, Nh, Nw, opts=_lib.options(list_builder=3)).cpu().numpy()
+    assert np.array_equal(a, b)
+
+
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
 def test_conv_dw_kernels_agree(case):
     """dW by the dense register-tile kernel and by the row-skipping kernel: the same sums in a different grouping."""

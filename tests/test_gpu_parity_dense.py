@@ -164,6 +164,27 @@ def test_dense_repeatable():
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
 
 
+@pytest.mark.parametrize("I", [1, 31, 32, 33, 64, 100, 147, 255, 256])
+def test_dense_short_rows_by_the_register_network_match_the_row_sort(I):
+    """Rows of at most 256 inputs are sorted by a network in registers; the per-row radix sort forced through the
+    measurement build gives the same lists (equal inputs in index order), hence the same bits. Inputs include
+    ties and values that never spike."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    rng = np.random.default_rng(I)
+    x = np.round(np.exp(rng.random((37, I)) * 2), 2).astype(np.float32)
+    x[rng.random(x.shape) < 0.2] = 1e5
+    w = (rng.standard_normal((I + 1, 48)) * np.sqrt(15.0 / I)).astype(np.float32)
+    params = O.fc_params(biasvolt=1.0)
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    a = ops.snn_fc(xd, wd, params, opts=_lib.options(list_builder=1))
+    b = ops.snn_fc(xd, wd, params, opts=_lib.options(list_builder=3))
+    assert torch.equal(a, b) and torch.equal(b, ops.snn_fc(xd, wd, params))
+    bc = b.cpu().numpy()
+    P.check_forward(bc[:37], bc[37:], O.fc_forward(x, w, params, "f32"), O.fc_forward(x, w, params, "f64"), rows=x,
+                    what="short rows I=%d" % I)
+
+
 def test_walk_variants_agree_bit_for_bit():
     """The library picks among several walk kernels (output pairs, consecutive outputs per lane, strided outputs,
     1/2/4/8 outputs per lane); forced one by one through the measurement build they must give identical bits."""
