@@ -1,21 +1,24 @@
-// SNN-TC forward (SnnFc / SnnCv) for sm_100a: gather -> sort in shared memory -> sorted walk.
+// SNN-TC forward (SnnFc / SnnCv) for sm_100a: sorted lists of the inputs that can spike -> sorted walk.
 //
 // Rows are dense samples or conv receptive fields (gathered straight from the NHWC image with MAX
-// outside it). Two kernels, joined by a scratch buffer of sorted lists in global memory:
-//   1. gather (sort kernel, one warp per row): inputs above MAX-0.1 ("never spikes") are dropped, the rest
-//      are kept as 32-bit sortable value bits plus a 16-bit source index in shared memory; conv rows find
-//      their taps through a per-CTA table, with predicated loads and no divergent branch;
-//   2. sort: the keys are rebased to the row's smallest, the 8-bit digits that the row's range needs are
-//      counted, and a stable least-significant-digit radix sort runs over those digits only (a last digit
-//      of one or two bits is a ballot split); rows of <= 32 inputs are ranked with shuffles, rows too long
-//      for two shared-memory buffers fall back to a CTA-wide in-place bitonic network;
-//   3. walk (walk kernels): every warp takes (row, block of outputs) items and walks the row's sorted list.
-//      The running sum(w)-theta and sum(w*x) stay in registers, in sorted order, bias first, with the
-//      arithmetic of the reference kernel (snntc/snnfc_kernels.cu.cc:33-69); the causality test is the
-//      sign of ysum - x*wsum per step, backed by the reference's exact division-free comparisons whenever
-//      it turns non-positive in any lane (see walk_row). Three layouts of a lane's outputs: a pair in one
-//      64-bit register (walk_row2, fan-out <= 64), 2 or 4 consecutive outputs read by one 8/16-byte load,
-//      or outputs lane + 32*m (odd fan-out, unaligned weights).
+// outside it). A scratch buffer of sorted lists in global memory -- per row the inputs at or below MAX-0.1 as
+// (value, element offset of the weight row), ascending -- joins two stages:
+//   1. the lists. Stride-1 convolutions up to 3x3 on 16 to 512 channels: per-pixel sort and two levels of
+//      merging (snntc_lists.cu). Rows of at most 256 inputs: a sorting network in registers, one warp per row
+//      (snntc_lists.cu). Everything else, here: one warp per row gathers the row into shared memory as 32-bit
+//      sortable value bits plus a 16-bit source index (conv rows find their taps through a per-CTA table, with
+//      predicated loads and no divergent branch), rebases the keys to the row's smallest, counts the 8-bit digits
+//      that the row's range needs and runs a stable least-significant-digit radix sort over those digits only (a
+//      last digit of one or two bits is a ballot split); rows too long for two shared-memory buffers fall back
+//      to a CTA-wide in-place bitonic network;
+//   2. the walk (walk kernels): every warp takes (row, block of outputs) items and walks the row's list, which it
+//      stages through shared memory 32 entries at a time. The running sum(w)-theta and sum(w*x) stay in
+//      registers, in sorted order, bias first, with the arithmetic of the reference kernel
+//      (snntc/snnfc_kernels.cu.cc:33-69); the causality test is the sign of q = ysum - x*wsum per step -- one FMA
+//      per output, the lane's smallest q as an integer, one warp vote -- backed by the reference's exact
+//      division-free comparisons whenever it turns non-positive in any lane (see walk_row). Three layouts of a
+//      lane's outputs: a pair in one 64-bit register (walk_row2, fan-out <= 64), 2 or 4 consecutive outputs read
+//      by one 8/16-byte load, or outputs lane + 32*m (odd fan-out, unaligned weights).
 #include "snntc_common.cuh"
 
 #include <limits.h>
