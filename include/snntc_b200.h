@@ -207,9 +207,16 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *                        only chooses between two schedules of the same kernels. Entry points may be called
  *                        from several host threads and on several streams at once: the library keeps no state
  *                        between calls apart from per-device caches behind a lock.
+ *   snntc_walk_copy_timeouts  The forward walk of layers whose weights fit (64 outputs x all fan-in rows within one
+ *                        CTA's shared memory) stages them there with asynchronous bulk copies and waits for them
+ *                        with a time limit; a CTA whose copies have not arrived in about a second reads the
+ *                        weights from global memory instead (same results) and counts here. Returns the count on
+ *                        the current device since the library was loaded (synchronises the device): 0 in a healthy
+ *                        process.
  */
 SNNTC_API unsigned long long snntc_launch_count(void);
 SNNTC_API void snntc_set_overlap(int on);
+SNNTC_API unsigned long long snntc_walk_copy_timeouts(void);
 
 #ifdef SNNTC_MEASURE
 /* ------------------------------------------------------------------------------------------------

@@ -23,6 +23,9 @@ struct Geometry {
   // inference only, may be null: I+2 counters. khist[k] += 1 for every output that fired after consuming k inputs
   // (the bias input is not counted), khist[I+1] += 1 for every output that did not fire.
   int* khist;
+  // forward only, set by launch_forward: one float, an upper bound on sum_i |w_ij| over every output j (the walk
+  // derives from it how close to zero its sign test must hand over to the reference's rounded comparisons)
+  const float* wbound;
 };
 
 struct LaunchInfo {
@@ -37,6 +40,7 @@ struct Options {
   int forward_parts = 3;    // bit 0: build the sorted lists, bit 1: walk them
   int walk_layout = 0;      // 0 auto, 1 output pairs, 2 outputs lane+32m, 3 consecutive outputs per lane;
                             // +4: read list entries straight from global memory instead of through shared memory
+                            // +8: output pairs with the weights staged in shared memory (where they fit)
   int walk_outputs = 0;     // 0 auto, 1..4: 1, 2, 4, 8 outputs per lane (pairs layout: 2 only)
   int list_builder = 0;     // 0 auto, 1 per-row radix sort, 2 per-pixel sort + merges (3x3 stride-1 conv only),
                             // 3 per-row sorting network in registers (rows of at most 256 inputs);
@@ -77,6 +81,8 @@ typedef uint2 WalkEntry;
 
 // ---- forward ---------------------------------------------------------------------------------
 size_t forward_workspace_bytes(const Geometry& g);
+// CTAs of the walk that gave up waiting for their weight copies (current device, since the library was loaded)
+unsigned long long walk_copy_timeouts();
 int launch_forward(const Geometry& g, const float* x, const float* w, float* out, void* ws, size_t ws_bytes,
                    const LaunchInfo& li, const Options& opt, cudaStream_t s);
 

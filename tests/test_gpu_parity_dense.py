@@ -198,8 +198,19 @@ def test_walk_variants_agree_bit_for_bit():
         for outputs in (0, 1, 2, 3, 4):
             out = ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=layout, walk_outputs=outputs))
             assert torch.equal(out, ref), "layout %d, outputs-per-lane choice %d" % (layout, outputs)
+    # the pairs walk with the weights of 64 outputs staged in shared memory by asynchronous bulk copies (8, 12: with and
+    # without staged list entries), one and several slices of 64 outputs, with and without bias row, more rows than warps
+    for (B, I, J, bv) in ((50, 300, 256, 1.0), (2100, 37, 64, 1.0), (70, 577, 128, 0.0), (3, 799, 64, 1.0)):
+        x, w = P.make_inputs(73 + I, (B, I), (I + (1 if bv else 0), J), "cfg")
+        prm = O.fc_params(biasvolt=bv)
+        xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+        ref = ops.snn_fc(xd, wd, prm, opts=_lib.options(walk_layout=1))
+        for layout in (8, 12):
+            assert torch.equal(ops.snn_fc(xd, wd, prm, opts=_lib.options(walk_layout=layout)), ref), (B, I, J, bv, layout)
+    assert _lib.load_measure().snntc_walk_copy_timeouts() == 0
     # a fan-out that leaves the last block of eight-per-lane outputs partly empty
     x, w = P.make_inputs(72, (20, 100), (101, 1000), "test")
+    params = O.fc_params(biasvolt=1.0)
     xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
     ref = ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=2, walk_outputs=1))
     for outputs in (2, 3, 4):
