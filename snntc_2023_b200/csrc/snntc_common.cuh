@@ -23,9 +23,11 @@ struct Geometry {
   // inference only, may be null: I+2 counters. khist[k] += 1 for every output that fired after consuming k inputs
   // (the bias input is not counted), khist[I+1] += 1 for every output that did not fire.
   int* khist;
-  // forward only, set by launch_forward: one float, an upper bound on sum_i |w_ij| over every output j (the walk
-  // derives from it how close to zero its sign test must hand over to the reference's rounded comparisons)
+  // forward only, set by launch_forward: wbound_n (<= 32) floats whose sum is an upper bound on sum_i |w_ij| for
+  // every output j (the walk derives from it how close to zero its sign test must hand over to the reference's
+  // rounded comparisons)
   const float* wbound;
+  int wbound_n;
 };
 
 struct LaunchInfo {

@@ -65,23 +65,27 @@ __device__ __forceinline__ int imin3(int a, int b, int c) { return min(min(a, b)
 // ysum against the ROUNDED product x*wsum (ratio_gt / ratio_le below), so it can see "ysum <= x*wsum" while the
 // exact difference is still positive by up to half an ulp of the product, and the other way round for the test
 // against the previous input. The walk therefore hands a step over to the reference's comparisons whenever
-// q <= tol, tol = 2^-21 * |x| * (|theta| + B), B = *g.wbound >= sum_i |w_ij| for every output j: |wsum| never
+// q <= tol, tol = 2^-21 * |x| * (|theta| + B), B = sum of g.wbound[] >= sum_i |w_ij| for every output j: |wsum| never
 // exceeds |theta| + B, so tol is at least eight times the largest rounding error of the product, and small enough
 // to be met by chance about once in 10^5 output steps. Compared as integers: tol >= +0, negative q are negative.
 __device__ __forceinline__ float walk_tolerance_base(const Geometry& g) {
-  return 4.76837158203125e-7f * (fabsf(g.theta) + __ldg(g.wbound));
+  const int lane = threadIdx.x & 31;
+  float b = lane < g.wbound_n ? __ldg(g.wbound + lane) : 0.f;
+#pragma unroll
+  for (int d = 16; d >= 1; d >>= 1) b += __shfl_xor_sync(0xffffffffu, b, d);
+  return 4.76837158203125e-7f * (fabsf(g.theta) + b) * 1.0001f;   // (a little slack for the rounding of the sums)
 }
 
-// *bound += sum over this CTA's weight rows of max_j |w_ij|: summed over all CTAs an upper bound on every column's
-// sum of magnitudes. rows = I + bias row. *bound must be zero before the launch.
-constexpr int kBoundRowsPerCta = 64;
+// bound[blockIdx.x] = sum over this CTA's weight rows of max_j |w_ij|: summed over the CTAs an upper bound on every
+// column's sum of magnitudes. rows = I + bias row; CTA c takes rows [c * rows_per_cta, (c + 1) * rows_per_cta).
+constexpr int kBoundMaxCtas = 32;
 __global__ void __launch_bounds__(256)
-snn_wbound_kernel(const float* __restrict__ w, int rows, int J, float* __restrict__ bound) {
+snn_wbound_kernel(const float* __restrict__ w, int rows, int J, int rows_per_cta, float* __restrict__ bound) {
   __shared__ float part[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int r0 = blockIdx.x * kBoundRowsPerCta;
+  const int r0 = blockIdx.x * rows_per_cta;
   float acc = 0.f;                                     // lane 0: sum of the row maxima of this warp's rows
-  for (int r = r0 + warp; r < min(rows, r0 + kBoundRowsPerCta); r += 8) {
+  for (int r = r0 + warp; r < min(rows, r0 + rows_per_cta); r += 8) {
     const float* wr = w + (size_t)r * J;
     float m = 0.f;
     for (int j = lane; j < J; j += 32) m = fmaxf(m, fabsf(__ldg(wr + j)));
@@ -95,7 +99,7 @@ snn_wbound_kernel(const float* __restrict__ w, int rows, int J, float* __restric
     float t = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) t += part[k];
-    atomicAdd(bound, t * 1.0001f);                     // (the order of the additions varies: a little slack covers it)
+    bound[blockIdx.x] = t;
   }
 }
 
@@ -222,23 +226,29 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
   // One chunk of CH steps: entries, then their weight rows, then the arithmetic. `fetch(i)` returns entry i of
   // the part of the list at hand.
   bool all_done = false;
-  auto chunk = [&](auto fetch, int k0) {
+  auto check_done = [&]() {
+    int any_live = 0;
+#pragma unroll
+    for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
+    all_done = !__any_sync(0xffffffffu, any_live != 0);
+  };
+  // `fetch2(i)` returns entries i and i+1 (i even) of the part of the list at hand as one 16-byte read.
+  static_assert(CH % 2 == 0, "entries are fetched two at a time");
+  auto chunk = [&](auto fetch2, int k0) {
     float xs[CH];
     float wv[CH][JPT];
 #pragma unroll
-    for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = fetch(k0 + u);
-      xs[u] = __uint_as_float(e.x);
-      load_weights(e.y, wv[u]);
+    for (int u = 0; u < CH; u += 2) {
+      const uint4 e2 = fetch2(k0 + u);
+      xs[u] = __uint_as_float(e2.x);
+      load_weights(e2.y, wv[u]);
+      xs[u + 1] = __uint_as_float(e2.z);
+      load_weights(e2.w, wv[u + 1]);
     }
     qlim = __float_as_int(tolbase * fmaxf(fabsf(xs[0]), fabsf(xs[CH - 1])));   // inputs ascend: |x| peaks at an end
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], u == 0 ? xprev : xs[u > 0 ? u - 1 : 0], wv[u]);
     xprev = xs[CH - 1];   // the previous input is only read when an output is about to fire: no copy per step
-    int any_live = 0;
-#pragma unroll
-    for (int m = 0; m < JPT; ++m) any_live |= livemask[m];
-    all_done = !__any_sync(0xffffffffu, any_live != 0);
   };
   auto single = [&](const WalkEntry e) {
     float wv[JPT];
@@ -260,15 +270,20 @@ __device__ __forceinline__ void walk_row(const Geometry& g, const WalkEntry* __r
       if (base + 32 + lane < nvalid) pre = __ldcg(ents + base + 32 + lane);
       const int nb = min(32, nvalid - base);
       const WalkEntry* cur = sbuf + b;
+      auto fetch2 = [&](int i) { return *reinterpret_cast<const uint4*>(cur + i); };
       int kk = 0;
-      for (; kk + CH <= nb && !all_done; kk += CH) chunk([&](int i) { return cur[i]; }, kk);
-      if (!all_done)
-        for (; kk < nb; ++kk) single(cur[kk]);
+#pragma unroll 1
+      for (; kk + CH <= nb; kk += CH) chunk(fetch2, kk);
+      for (; kk < nb; ++kk) single(cur[kk]);
+      check_done();   // one "has every output fired" vote per block
     }
   } else {
     int k = 0;
-    for (; k + CH <= nvalid && !all_done; k += CH)
-      chunk([&](int i) { return __ldcg(ents + i); }, k);   // list entries bypass L1: it is kept for the weights
+    for (; k + CH <= nvalid && !all_done; k += CH) {
+      // list entries bypass L1: it is kept for the weights
+      chunk([&](int i) { return __ldcg(reinterpret_cast<const uint4*>(ents + i)); }, k);
+      check_done();
+    }
     if (!all_done)
       for (; k < nvalid; ++k) single(__ldcg(ents + k));
   }
@@ -431,23 +446,28 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       for (int m = 0; m < JP; ++m) wv[m] = load_pair(wrow, m);
     }
   };
-  auto chunk = [&](auto fetch, int k0) {
+  auto check_done = [&]() {
+    int any_live = 0;
+#pragma unroll
+    for (int m = 0; m < 2 * JP; ++m) any_live |= live[m];
+    all_done = !__any_sync(0xffffffffu, any_live != 0);
+  };
+  static_assert(CH % 2 == 0, "entries are fetched two at a time");
+  auto chunk = [&](auto fetch2, int k0) {
     float xs[CH];
     uint64_t wv[CH][JP];
 #pragma unroll
-    for (int u = 0; u < CH; ++u) {
-      const WalkEntry e = fetch(k0 + u);
-      xs[u] = __uint_as_float(e.x);
-      load_row(e.y, wv[u]);
+    for (int u = 0; u < CH; u += 2) {
+      const uint4 e2 = fetch2(k0 + u);
+      xs[u] = __uint_as_float(e2.x);
+      load_row(e2.y, wv[u]);
+      xs[u + 1] = __uint_as_float(e2.z);
+      load_row(e2.w, wv[u + 1]);
     }
     qlim = __float_as_int(tolbase * fmaxf(fabsf(xs[0]), fabsf(xs[CH - 1])));   // inputs ascend: |x| peaks at an end
 #pragma unroll
     for (int u = 0; u < CH; ++u) step(xs[u], u == 0 ? xprev : xs[u > 0 ? u - 1 : 0], wv[u]);
     xprev = xs[CH - 1];
-    int any_live = 0;
-#pragma unroll
-    for (int m = 0; m < 2 * JP; ++m) any_live |= live[m];
-    all_done = !__any_sync(0xffffffffu, any_live != 0);
   };
   auto single = [&](const WalkEntry e) {
     uint64_t wv[JP];
@@ -472,15 +492,20 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
       if (base + 32 + lane < nvalid) pre = __ldcg(ents + base + 32 + lane);
       const int nb = min(32, nvalid - base);
       const WalkEntry* cur = sbuf + b;
+      auto fetch2 = [&](int i) { return *reinterpret_cast<const uint4*>(cur + i); };
       int kk = 0;
-      for (; kk + CH <= nb && !all_done; kk += CH) chunk([&](int i) { return cur[i]; }, kk);
-      if (!all_done)
-        for (; kk < nb; ++kk) single(cur[kk]);
+#pragma unroll 1
+      for (; kk + CH <= nb; kk += CH) chunk(fetch2, kk);
+      for (; kk < nb; ++kk) single(cur[kk]);
+      check_done();   // one "has every output fired" vote per block
     }
   } else {
     int k = 0;
-    for (; k + CH <= nvalid && !all_done; k += CH)
-      chunk([&](int i) { return __ldcg(ents + i); }, k);   // list entries bypass L1: it is kept for the weights
+    for (; k + CH <= nvalid && !all_done; k += CH) {
+      // list entries bypass L1: it is kept for the weights
+      chunk([&](int i) { return __ldcg(reinterpret_cast<const uint4*>(ents + i)); }, k);
+      check_done();
+    }
     if (!all_done)
       for (; k < nvalid; ++k) single(__ldcg(ents + k));
   }
@@ -987,7 +1012,7 @@ template <int JPT, bool VECW, bool STAGE>
 __global__ void __launch_bounds__(kFwdThreads, JPT <= 4 ? 4 : 1)   // up to four outputs per lane: 64 registers, 32 warps per SM
 snn_walk_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                 const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
-  __shared__ WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
+  __shared__ __align__(16) WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
   WalkEntry* sbuf = stage + (STAGE ? (threadIdx.x >> 5) * 64 : 0);
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
@@ -1016,7 +1041,7 @@ template <int JP, bool STAGE>
 __global__ void __launch_bounds__(kFwdThreads)
 snn_walk2_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g, int istride,
                  const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end) {
-  __shared__ WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
+  __shared__ __align__(16) WalkEntry stage[STAGE ? kFwdWarps * 64 : 1];   // two blocks of 32 list entries per warp
   WalkEntry* sbuf = stage + (STAGE ? (threadIdx.x >> 5) * 64 : 0);
   const int J = g.J, R = g.R;
   const int lane = threadIdx.x & 31;
@@ -1238,9 +1263,11 @@ int launch_forward(const Geometry& g_in, const float* x, const float* w, float* 
 
   const int fparts = opt.forward_parts;
   if (fparts & 2) {   // the walk's bound on the weight sums (see walk_tolerance_base)
-    if (cudaMemsetAsync(wbound, 0, sizeof(float), s) != cudaSuccess) return E_CUDA;
     const int rows_w = g.I + g.has_bias;
-    snn_wbound_kernel<<<(rows_w + kBoundRowsPerCta - 1) / kBoundRowsPerCta, 256, 0, s>>>(w, rows_w, g.J, wbound);
+    int per = (rows_w + kBoundMaxCtas - 1) / kBoundMaxCtas;
+    per = (per + 7) & ~7;                                // whole rounds of the CTA's eight warps
+    g.wbound_n = (rows_w + per - 1) / per;
+    snn_wbound_kernel<<<g.wbound_n, 256, 0, s>>>(w, rows_w, g.J, per, wbound);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
@@ -1286,11 +1313,12 @@ int launch_forward(const Geometry& g_in, const float* x, const float* w, float* 
   if (variant == 3 && jsel == 2 && !al16) jsel = 1;
   size_t smemw_bytes = 0;
   int smemw_shift = 0;
-  // weights staged in shared memory: where they fit, for fan-out 64 and 128 with enough rows to keep one CTA of 32
-  // warps per SM busy (measured 13-16 % faster than the global-memory pairs walk at fan-out 64, 6 % faster than
-  // four outputs per lane at fan-out 128); walk_layout 8 asks for it wherever it fits, a named layout switches it off
+  // weights staged in shared memory: where they fit, for fan-out 64 with enough rows to keep one CTA of 32 warps
+  // per SM busy (measured 13-16 % faster than the global-memory pairs walk; at fan-out 128 four outputs per lane
+  // from global memory are 5 % faster than two staged slices); walk_layout 8 asks for it wherever it fits, a named
+  // layout switches it off
   const bool smemw = walk_smemw_ok(g, w, li, &smemw_bytes, &smemw_shift) &&
-                     ((opt.walk_layout & 8) != 0 || ((opt.walk_layout & 3) == 0 && g.J <= 128 && g.R >= 8192));
+                     ((opt.walk_layout & 8) != 0 || ((opt.walk_layout & 3) == 0 && g.J == 64 && g.R >= 8192));
   auto walk = [&](cudaStream_t st, int r0, int r1) -> int {
     if (!(fparts & 2)) return OK;
     if (smemw) return launch_walk2_smemw(g, keys_g, nvalid_g, w, out, li, st, r0, r1, stage, smemw_bytes, smemw_shift);
