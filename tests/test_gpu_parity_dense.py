@@ -248,6 +248,59 @@ def test_dense_exact_ties_between_spike_time_and_next_input(J, bv):
     np.testing.assert_allclose(out[64:][fired_ref], ref["inv"][fired_ref], rtol=2e-6, atol=0)
 
 
+def _rounded_product_rows(w0, n, seed):
+    """Rows (x0, x1, x2) for a no-bias output with first weight w0 and threshold 1: after x0 the sums are
+    (w0 - 1, x0*w0); x1 is chosen so that ysum is ABOVE the exact product x1*wsum but not above the product rounded to
+    fp32 -- the reference, which compares against the rounded product, fires at x1; the exact sign of ysum - x1*wsum
+    says "not yet"."""
+    f32 = np.float32
+    rng = np.random.default_rng(seed)
+    ws = f32(f32(w0) - f32(1.0))
+    rows = []
+    while len(rows) < n:
+        x0 = f32(rng.uniform(1.0, 3.0))
+        ys = f32(np.float64(x0) * np.float64(f32(w0)))
+        x1 = f32(np.float64(ys) / np.float64(ws))
+        for _ in range(2):
+            x1 = np.nextafter(x1, f32(-np.inf))
+        for _ in range(5):
+            prod = np.float64(x1) * np.float64(ws)
+            if x1 > x0 and ys > f32(np.float64(x0) * np.float64(ws)) and np.float64(ys) > prod and ys <= f32(prod):
+                rows.append((x0, x1, f32(x1 * f32(1.5))))
+                break
+            x1 = np.nextafter(x1, f32(np.inf))
+    return np.array(rows, np.float32)
+
+
+@pytest.mark.parametrize("J", [4, 64, 128, 256])
+def test_dense_decision_by_the_rounded_product_like_the_reference(J):
+    """The reference decides "spike time <= next input" as ysum <= fl(x*wsum) (snntc/snnfc_kernels.cu.cc:46-48): it
+    can fire while the exact difference ysum - x*wsum is still positive by less than the rounding of the product.
+    The walk's sign test alone would miss that step; its margin hands it to the reference's comparison. Constructed
+    rows where that happens for output 0, every walk layout, results bit for bit those of the fp32 restatement."""
+    import torch
+    from snntc_2023_b200 import _lib, ops
+    x = _rounded_product_rows(2.3, 96, J)
+    rng = np.random.default_rng(J)
+    w = rng.uniform(-1.0, 1.5, (3, J)).astype(np.float32)
+    w[:, 0] = (2.3, 0.7, 0.9)
+    params = O.fc_params(biasvolt=0.0)
+    ref = O.fc_forward(x, w, params, "f32")
+    assert np.all(ref["k"][:, 0] == 1), "the reference consumes one input and fires at the second"
+    xd, wd = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda()
+    outs = [ops.snn_fc(xd, wd, params)]
+    outs += [ops.snn_fc(xd, wd, params, opts=_lib.options(walk_layout=lay)) for lay in (1, 2, 3, 8)]
+    fired = ref["y"] < 1e5 - 0.1
+    assert fired[:, 0].all()
+    for o in outs:
+        assert torch.equal(o, outs[0])                               # every layout: the same bits
+        o = o.cpu().numpy()
+        assert np.array_equal(o[:96] < 1e5 - 0.1, fired)
+        # 1/(sum w - theta) tells which inputs were consumed: 1/1.3 at the second input, 1/2.0 one input later
+        np.testing.assert_allclose(o[96:][fired], ref["inv"][fired], rtol=2e-6, atol=0)
+        np.testing.assert_allclose(o[:96][fired], ref["y"][fired], rtol=2e-6, atol=0)
+
+
 @pytest.mark.parametrize("J", [2, 64, 128, 256])
 def test_dense_inputs_below_the_bias_input_fire_with_negative_denominator(J):
     """The reference's tests are sign-safe (snntc/snnfc_kernels.cu.cc:36-38,53-55): with inputs BELOW the bias input
