@@ -207,16 +207,17 @@ SNNTC_API int snntc_fc_backward_noalloc(const float* grad_2BJ, const float* x, c
  *                        only chooses between two schedules of the same kernels. Entry points may be called
  *                        from several host threads and on several streams at once: the library keeps no state
  *                        between calls apart from per-device caches behind a lock.
- *   snntc_walk_copy_timeouts  The forward walk of layers whose weights fit (64 outputs x all fan-in rows within one
- *                        CTA's shared memory) stages them there with asynchronous bulk copies and waits for them
- *                        with a time limit; a CTA whose copies have not arrived in about a second reads the
- *                        weights from global memory instead (same results) and counts here. Returns the count on
- *                        the current device since the library was loaded (synchronises the device): 0 in a healthy
- *                        process.
+ *   snntc_copy_timeouts  Two kernels wait for asynchronous bulk copies, each wait with a time limit of about a second:
+ *                        the forward walk of layers whose weights fit in shared memory (64 outputs x all fan-in rows)
+ *                        waits for its weight slice and reads the weights from global memory instead when it does
+ *                        not arrive (same results); the weight-gradient kernel of stride-1 convolutions waits for
+ *                        the tiles of a stage and, when they do not arrive, stops and leaves its part of the
+ *                        gradient incomplete. Either way the CTA counts here. Returns the count on the current
+ *                        device since the library was loaded (synchronises the device): 0 in a healthy process.
  */
 SNNTC_API unsigned long long snntc_launch_count(void);
 SNNTC_API void snntc_set_overlap(int on);
-SNNTC_API unsigned long long snntc_walk_copy_timeouts(void);
+SNNTC_API unsigned long long snntc_copy_timeouts(void);
 
 #ifdef SNNTC_MEASURE
 /* ------------------------------------------------------------------------------------------------

@@ -27,7 +27,7 @@ SYMBOLS = {
     "snntc_cv_backward": (_INT, [_F] * 8 + [_INT] * 10 + [_F, _SZ, _F]),
     "snntc_launch_count": (ctypes.c_ulonglong, []),
     "snntc_set_overlap": (None, [_INT]),
-    "snntc_walk_copy_timeouts": (ctypes.c_ulonglong, []),
+    "snntc_copy_timeouts": (ctypes.c_ulonglong, []),
     "snntc_minpool_forward": (_INT, [_F, _F, _F] + [_INT] * 12 + [ctypes.c_float, _F]),
     "snntc_minpool_backward": (_INT, [_F, _F, _F] + [_INT] * 12 + [_F]),
     "snntc_fc_backward_noalloc": (_INT, [_F] * 8 + [_INT] * 4 + [_F]),

@@ -19,7 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libsnntc_b200.so")
 LIB_MEASURE = os.path.join(HERE, "libsnntc_b200_measure.so")
-SOURCES = ["snntc_forward.cu", "snntc_lists.cu", "snntc_backward.cu", "snntc_dw_skip.cu", "snntc_dx_sparse.cu", "snntc_pool.cu",
+SOURCES = ["snntc_forward.cu", "snntc_lists.cu", "snntc_backward.cu", "snntc_dw_skip.cu", "snntc_dw_tma.cu", "snntc_dx_sparse.cu", "snntc_pool.cu",
            "snntc_noalloc.cu", "snntc_train.cu", "snntc_api.cu"]
 API_SOURCE = "snntc_api.cu"   # the only file that reads SNNTC_MEASURE
 HEADERS = [os.path.join(CSRC, "snntc_common.cuh"), os.path.join(CSRC, "snntc_merge.cuh"),

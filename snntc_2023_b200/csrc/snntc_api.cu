@@ -276,7 +276,7 @@ unsigned long long snntc_launch_count(void) { return snntc::g_launches.load(std:
 
 void snntc_set_overlap(int on) { snntc::g_overlap.store(on ? 1 : 0, std::memory_order_relaxed); }
 
-unsigned long long snntc_walk_copy_timeouts(void) { return snntc::walk_copy_timeouts(); }
+unsigned long long snntc_copy_timeouts(void) { return snntc::walk_copy_timeouts() + snntc::dw_copy_timeouts(); }
 
 size_t snntc_fc_forward_workspace_bytes(int B, int I, int J) {
   snntc::Geometry g; memset(&g, 0, sizeof(g));

@@ -846,7 +846,7 @@ static float dw_scale(const Geometry& g) {
 static bool want_dw_skip(const Geometry& g, const Options& opt) {
   if (opt.dw_kernel == 1) return false;
   if (!g.is_conv || (g.C & 3) != 0 || (g.J & 3) != 0) return false;
-  if (opt.dw_kernel == 2) return true;
+  if (opt.dw_kernel >= 2) return true;
   return g.R >= 2048 && g.I >= 128;
 }
 
@@ -871,6 +871,10 @@ static BackwardLayout backward_layout(const Geometry& g, const LaunchInfo& li) {
     int rps = 0;
     const size_t skip = (size_t)dw_skip_splits(g, li, &rps) * plane;
     if (skip > part) part = skip;
+    if (dw_tma_shape_ok(g)) {
+      const size_t tma = (size_t)dw_tma_splits(g, li, &rps) * plane;
+      if (tma > part) part = tma;
+    }
   }
   if (g.I + g.has_bias <= 32 && g.R >= 4096) {   // the small fan-in kernel
     int rps = 0;
@@ -946,9 +950,15 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     float* partial = dw;
     if (want_dw_skip(g, opt) && dw_skip_supported(g, x, uv, out)) {
       int rps = 0;
-      splits = dw_skip_splits(g, li, &rps);
       partial = planes;   // always reduced from the workspace: its tiles are stored 16 bytes at a time
-      rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, li, s);
+      // tiles through tensor maps where the shape allows (dw_kernel 2: per-thread copies whatever the shape)
+      if (opt.dw_kernel != 2 && dw_tma_supported(g, x, uv, out)) {
+        splits = dw_tma_splits(g, li, &rps);
+        rc = launch_dw_tma(g, uv, x, out, partial, splits, rps, scale, exact_flag, li, s);
+      } else {
+        splits = dw_skip_splits(g, li, &rps);
+        rc = launch_dw_skip(g, uv, x, out, partial, splits, rps, scale, exact_flag, li, s);
+      }
       splits = splits < 1 ? 1 : splits;
       if (rc == OK) {
         int blocks = (int)((n + 255) / 256);

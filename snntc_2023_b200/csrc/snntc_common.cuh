@@ -48,7 +48,8 @@ struct Options {
                             // 3 per-row sorting network in registers (rows of at most 256 inputs);
                             // + 4*(k+1): the merges are cut into 2^k pieces each (k = 0 .. 5) instead of auto
   int backward_parts = 3;   // bit 0: dX, bit 1: dW
-  int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0)
+  int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0) with per-thread
+                            // copies, 4 the row-skipping kernel fed through tensor maps (where the shape allows)
   int dx_kernel = 0;        // 0 auto, 1 dense register tile, 2 list-walking kernel (conv, C % 4 == 0, C <= 512)
   int overlap = -1;         // -1 library setting (snntc_set_overlap), 0 one stream, 1 dX beside dW
 };
@@ -117,6 +118,16 @@ int dw_skip_splits(const Geometry& g, const LaunchInfo& li, int* rows_per_split)
 int launch_dw_skip(const Geometry& g, const float* uv, const float* x, const float* out, float* partial,
                    int splits, int rows_per_split, float scale, const int* exact_flag,
                    const LaunchInfo& li, cudaStream_t s);
+
+// The same kernel with its tiles brought in by tiled bulk copies through tensor maps (snntc_dw_tma.cu): stride-1
+// convolutions on a power-of-two number of channels (<= 256). Its slices are counted in stages of 16 fields.
+bool dw_tma_shape_ok(const Geometry& g);
+bool dw_tma_supported(const Geometry& g, const float* x, const float* uv, const float* out);
+int dw_tma_splits(const Geometry& g, const LaunchInfo& li, int* stages_per_split);
+int launch_dw_tma(const Geometry& g, const float* uv, const float* x, const float* out, float* partial, int splits,
+                  int stages_per_split, float scale, const int* exact_flag, const LaunchInfo& li, cudaStream_t s);
+// CTAs of that kernel that gave up waiting for their copies (current device, since the library was loaded)
+unsigned long long dw_copy_timeouts();
 
 // dX by a kernel that walks, per input pixel, the lists of outputs with a non-zero gradient factor
 // (snntc_dx_sparse.cu). dx_sparse_bytes is its scratch (lists, their lengths, transposed weights).

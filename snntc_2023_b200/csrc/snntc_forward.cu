@@ -1118,7 +1118,7 @@ snn_walk2_smemw_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, c
     bool arrived = false;
     while (!arrived && clock64() - t0 < kSmemwWaitClocks) {
       unsigned ok;
-      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                    : "=r"(ok) : "r"(bar) : "memory");
       arrived = ok != 0u;
     }

@@ -39,6 +39,11 @@ CONV_CASES = [
     (93, 3, 9, 7, 32, 3, 2, 1, 1, 48, 1.0, "VALID", "ref"),      # merged lists with a 3x2 kernel, VALID, odd sizes
     (94, 2, 6, 9, 20, 2, 3, 1, 1, 12, 0.0, "SAME", "test"),      # 2x3 kernel, asymmetric SAME padding, C not a multiple of 32
     (96, 2, 11, 9, 16, 3, 3, 2, 1, 24, 1.0, "SAME", "test"),     # strides 2x1: the list-walking dX kernel with strided taps
+    # shapes of the tensor-map dW kernel beyond the benchmark layers: a map 4 wide (boxes of four image rows), a 2x2
+    # kernel (SAME pads only below and right), 32 and 16 channels, a fan-out that is no multiple of 32
+    (97, 4, 4, 4, 32, 3, 3, 1, 1, 64, 1.0, "SAME", "ref"),
+    (98, 2, 16, 16, 16, 2, 2, 1, 1, 40, 1.0, "SAME", "cfg"),
+    (99, 3, 16, 2, 64, 3, 1, 1, 1, 32, 0.0, "SAME", "ref"),      # a map 2 wide, a 3x1 kernel, no bias
 ]
 
 
@@ -102,7 +107,7 @@ def test_conv_backward(case):
 
 
 # ---- kernel variants against each other (measurement build: the kernel choice of a call is given explicitly)
-VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 51, 82, 84, 86, 92, 93, 94, 96)]
+VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 51, 82, 84, 86, 92, 93, 94, 96, 97, 98, 99)]
 
 
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
@@ -165,6 +170,12 @@ def test_conv_dw_kernels_agree(case):
     # twice the same call: no atomics, identical bits
     _, dw3, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=2))
     assert torch.equal(dw2, dw3)
+    # the same kernel fed through tensor maps (where the shape allows; elsewhere this is the call above again)
+    _, dw5, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=4))
+    P.check_close(dw5.cpu().numpy(), ref["dw"], "row-skipping dW through tensor maps %s" % (case,), abs_sum=ref["dw_abs"])
+    _, dw6, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=4))
+    assert torch.equal(dw5, dw6)
+    assert _lib.load_measure().snntc_copy_timeouts() == 0
     # a value outside the range of the scaled inner loop (|u| >= 2^100) sends the kernel through its unscaled loop
     j_fired = int(np.argmax(outc[0, 0, 0, :] < 1e5 - 0.1))
     g[0, 0, 0, j_fired] = 4e30

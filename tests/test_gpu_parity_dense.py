@@ -207,7 +207,7 @@ def test_walk_variants_agree_bit_for_bit():
         ref = ops.snn_fc(xd, wd, prm, opts=_lib.options(walk_layout=1))
         for layout in (8, 12):
             assert torch.equal(ops.snn_fc(xd, wd, prm, opts=_lib.options(walk_layout=layout)), ref), (B, I, J, bv, layout)
-    assert _lib.load_measure().snntc_walk_copy_timeouts() == 0
+    assert _lib.load_measure().snntc_copy_timeouts() == 0
     # a fan-out that leaves the last block of eight-per-lane outputs partly empty
     x, w = P.make_inputs(72, (20, 100), (101, 1000), "test")
     params = O.fc_params(biasvolt=1.0)
