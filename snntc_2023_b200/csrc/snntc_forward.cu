@@ -345,13 +345,14 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // read back as 0 - nws: 1/(+0) = +inf clamps to "no spike", 1/(-0) would not. Requires J even and the
 // weights 8-byte aligned.
 // WS: the weights of this warp's 64 outputs sit in shared memory as [fan-in row][64] (see snn_walk2_smemw_kernel);
-// `ws_lane` is the shared-memory byte address of this lane's pair in row 0 and `jshift` = log2(J / 64), so that a list
-// entry's element offset (source index * J) becomes the row's offset in the slice by a shift. JP == 1 only.
+// `ws_lane` is the shared-memory byte address of this lane's pair in row 0 and `wmul` = 256 / J (J = 64, 128 or 256): a
+// list entry's element offset (source index * J) times wmul is the row's byte offset in the slice -- one integer
+// multiply-add on the FMA pipe per weight read. JP == 1 only.
 template <int JP, int CH, bool FULL, bool STAGE, bool WS = false>
 __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __restrict__ ents, int nvalid,
                                           const float* __restrict__ w, int jbase, int lane,
                                           float* __restrict__ y_row, float* __restrict__ inv_row,
-                                          WalkEntry* __restrict__ sbuf, unsigned ws_lane = 0u, int jshift = 0) {
+                                          WalkEntry* __restrict__ sbuf, unsigned ws_lane = 0u, unsigned wmul = 0u) {
   static_assert(!WS || JP == 1, "weights in shared memory: one output pair per lane");
   const int J = g.J;
   int jl[JP];
@@ -433,8 +434,7 @@ __device__ __forceinline__ void walk_row2(const Geometry& g, const WalkEntry* __
   bool all_done = false;
   auto load_row = [&](unsigned eoff, uint64_t (&wv)[JP]) {
     if constexpr (WS) {
-      // row offset in the slice: (eoff >> jshift) elements of 4 bytes = (eoff >> jshift) << 2 bytes
-      asm("ld.shared.b64 %0, [%1];" : "=l"(wv[0]) : "r"(ws_lane + ((eoff >> jshift) << 2)));
+      asm("ld.shared.b64 %0, [%1];" : "=l"(wv[0]) : "r"(eoff * wmul + ws_lane));
     } else if constexpr (JP == 1) {
       // one pair per lane: a 32-bit element offset from the (uniform) weight base measured faster than a
       // 64-bit per-lane pointer plus the entry's offset
@@ -1081,7 +1081,7 @@ template <bool STAGE>
 __global__ void __launch_bounds__(kSmemwThreads, 1)
 snn_walk2_smemw_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, const int* __restrict__ nvalid_g,
                        int istride, const float* __restrict__ w, float* __restrict__ out, int row_begin, int row_end,
-                       int jshift) {
+                       unsigned wmul) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   __shared__ __align__(8) unsigned long long copy_done;
   const int J = g.J, R = g.R;
@@ -1139,7 +1139,7 @@ snn_walk2_smemw_kernel(const Geometry g, const WalkEntry* __restrict__ keys_g, c
     const int n = __shfl_sync(0xffffffffu, __ldg(nvalid_g + r), 0);
     float* yr = y_out + (size_t)r * J;
     float* ir = inv_out ? inv_out + (size_t)r * J : nullptr;
-    if (staged) walk_row2<1, 8, true, STAGE, true>(g, krow, n, w, j0, lane, yr, ir, sbuf, ws_lane, jshift);
+    if (staged) walk_row2<1, 8, true, STAGE, true>(g, krow, n, w, j0, lane, yr, ir, sbuf, ws_lane, wmul);
     else walk_row2<1, 8, true, STAGE, false>(g, krow, n, w, j0, lane, yr, ir, sbuf);
     if (STAGE) __syncwarp();
   }
@@ -1186,22 +1186,20 @@ int launch_walk2(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g
 
 // The pairs walk with the weights staged in shared memory: fan-out a power-of-two multiple of 64, weights 16-byte
 // aligned, all (I + bias) rows of a 64-output slice plus the list staging buffers within one CTA's shared memory.
-bool walk_smemw_ok(const Geometry& g, const float* w, const LaunchInfo& li, size_t* smem_bytes, int* jshift) {
-  if (g.J < 64 || (g.J & (g.J - 1)) != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
+bool walk_smemw_ok(const Geometry& g, const float* w, const LaunchInfo& li, size_t* smem_bytes, int* wmul) {
+  if ((g.J != 64 && g.J != 128 && g.J != 256) || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
   const size_t rows_w = (size_t)g.I + g.has_bias;
   const size_t smem = rows_w * 256 + (size_t)kSmemwWarps * 64 * sizeof(WalkEntry);
   if (smem + 2048 > (size_t)li.max_smem_optin || rows_w * 256 >= (1u << 20)) return false;
   if ((g.J >> 6) > li.num_sms) return false;
-  int sh = 0;
-  while ((64 << sh) < g.J) ++sh;
   *smem_bytes = smem;
-  *jshift = sh;
+  *wmul = 256 / g.J;
   return true;
 }
 
 int launch_walk2_smemw(const Geometry& g, const WalkEntry* keys_g, const int* nvalid_g, const float* w, float* out,
                        const LaunchInfo& li, cudaStream_t s, int row_begin, int row_end, bool stage, size_t smem,
-                       int jshift) {
+                       int wmul) {
   const int slices = g.J >> 6;
   const long rows = row_end - row_begin;
   long per_slice = li.num_sms / slices;                       // persistent: one CTA per SM
@@ -1212,11 +1210,11 @@ int launch_walk2_smemw(const Geometry& g, const WalkEntry* keys_g, const int* nv
   if (stage) {
     if (cudaFuncSetAttribute(snn_walk2_smemw_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return E_CUDA;
-    snn_walk2_smemw_kernel<true><<<grid, kSmemwThreads, smem, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end, jshift);
+    snn_walk2_smemw_kernel<true><<<grid, kSmemwThreads, smem, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end, (unsigned)wmul);
   } else {
     if (cudaFuncSetAttribute(snn_walk2_smemw_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return E_CUDA;
-    snn_walk2_smemw_kernel<false><<<grid, kSmemwThreads, smem, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end, jshift);
+    snn_walk2_smemw_kernel<false><<<grid, kSmemwThreads, smem, s>>>(g, keys_g, nvalid_g, key_stride(g), w, out, row_begin, row_end, (unsigned)wmul);
   }
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
