@@ -691,10 +691,10 @@ def run_gpu_arm(args):
         total_ms = sum(v[0] for v in kinds.values()) or 1.0
         dom = max(kinds, key=lambda k: kinds[k][0])
         dms, dflops, dn = kinds[dom]
-        names = {"lists": "snn_pixel_runs_kernel+snn_row_runs_kernel+snn_field_lists_kernel (3x3 stride-1 conv) / snn_sort_kernel",
-                 "walk": "snn_walk_kernel/snn_walk2_kernel",
+        names = {"lists": "snn_pixel_runs_kernel+snn_row_runs_kernel+snn_field_lists_kernel (3x3 stride-1 conv) / snn_small_rows_kernel / snn_sort_kernel",
+                 "walk": "snn_walk_kernel/snn_walk2_smemw_kernel/snn_walk2_kernel(+snn_wbound_kernel)",
                  "dx": "snn_dx_sparse_kernel(+snn_act_lists_kernel, snn_weight_transpose_kernel)/snn_dx_wide_kernel/snn_dx_kernel(+snn_u_kernel)",
-                 "dw": "snn_dw_skip_kernel/snn_dw_kernel(+snn_u_kernel, snn_dw_reduce_kernel)"}
+                 "dw": "snn_dw_tma_kernel/snn_dw_skip_kernel/snn_dw_small_kernel/snn_dw_kernel(+snn_u_kernel, snn_dw_reduce_kernel)"}
         traffic, traffic_stale = None, None
         try:
             tj = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
