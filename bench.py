@@ -228,7 +228,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
@@ -802,11 +802,28 @@ def run_gpu_arm(args):
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
-        print(json.dumps(line), flush=True)
+        emit(line)
+
+
+_RESULT_OUT = None
+
+
+def emit(line):
+    """The one JSON line, written to the process's original standard output."""
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
+    global _RESULT_OUT
     args = parse_args()
+    # Standard output carries exactly one line, the result. Libraries that write there on their own (NCCL prints its
+    # version line to file descriptor 1) are sent to standard error: descriptor 1 is pointed at descriptor 2 for the
+    # rest of the process and the result goes to a duplicate of the original.
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
     else:
