@@ -39,7 +39,7 @@ def pytest_sessionfinish(session, exitstatus):
     if not parity.REPORT:
         return
     try:
-        parity.dump_report(os.path.join(ROOT, "gpurun_out", "parity_report.json"))
+        parity.dump_report(os.path.join(ROOT, os.environ.get("SNNTC_REPORT_DIR", "gpurun_out"), "parity_report.json"))
     except OSError:
         pass
     print("\nparity summary: %s" % (parity.summary(),))

@@ -166,7 +166,7 @@ def test_objective_with_constraint_cost_reaches_the_flat_gradient():
 
 def test_data_parallel_gradient_equals_full_batch_gradient():
     """What the all-reduce of a data-parallel step computes, on one GPU: the mean of the shards' flat gradients
-    against the gradient of the whole batch (SURVEY protocol: relative L2 <= 1e-5)."""
+    against the gradient of the whole batch (same bound as the operators' gradients: relative L2 <= 1e-5)."""
     import torch
     from snntc_2023_b200 import ddp, nets
     specs = nets.CIFAR_CNN
