@@ -68,12 +68,95 @@ __device__ __forceinline__ void warp_bitonic_sort(u64 (&v)[EPL], int lane) {
   }
 }
 
+// Sort of 32*EPL keys for an EPL that is no power of two (the bitonic network above would round it up: 160 keys
+// would be sorted as 256). Every lane sorts its own EPL keys; the lanes then run the bitonic network over their
+// BLOCKS, a compare-exchange being a merge-split: against the partner's block in reverse, min(mine[i], theirs[EPL-1-i])
+// over i are the EPL smallest keys of both blocks, the maxima the EPL largest; what a lane keeps is sorted again
+// (odd-even transposition: EPL (EPL - 1) / 2 exchanges). Same result layout: element lane*EPL + m has rank lane*EPL + m.
+template <int EPL>
+__device__ __forceinline__ void lane_sort(u64 (&v)[EPL]) {
+#pragma unroll
+  for (int round = 0; round < EPL; ++round) {
+#pragma unroll
+    for (int i = round & 1; i + 1 < EPL; i += 2) {
+      const u64 a = v[i], b = v[i + 1];
+      const bool sw = a > b;
+      v[i] = sw ? b : a;
+      v[i + 1] = sw ? a : b;
+    }
+  }
+}
+template <int EPL>
+__device__ __forceinline__ void warp_block_sort(u64 (&v)[EPL], int lane) {
+  lane_sort<EPL>(v);
+#pragma unroll
+  for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+    for (int j = k >> 1; j >= 1; j >>= 1) {
+      const bool lower = (lane & j) == 0;
+      const bool asc = (lane & k) == 0 || k == 32;
+      const bool keep_low = asc == lower;
+      u64 o[EPL];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) o[i] = __shfl_xor_sync(0xffffffffu, v[EPL - 1 - i], j);
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const bool o_less = o[i] < v[i];
+        v[i] = (keep_low == o_less) ? o[i] : v[i];
+      }
+      lane_sort<EPL>(v);
+    }
+  }
+}
+template <int EPL>
+__device__ __forceinline__ void warp_sort(u64 (&v)[EPL], int lane) {
+  if constexpr ((EPL & (EPL - 1)) == 0) warp_bitonic_sort<EPL>(v, lane);
+  else warp_block_sort<EPL>(v, lane);
+}
+
+// Sorts the n <= 32*EPL real keys of v (the other slots hold ~0) and writes them as a run. A pixel that has at most
+// half its slots filled -- most pixels of a hidden layer: about half of a layer's inputs never spike -- is first
+// compacted through `buf` (16*EPL keys of shared memory per warp) into half the slots, again and again if it can
+// be, so that the network it goes through fits its real keys, not its channel count.
+template <int EPL>
+__device__ __forceinline__ void sort_and_write_run(u64 (&v)[EPL], int n, int lane, u64* __restrict__ buf,
+                                                   WalkEntry* __restrict__ dst, int J) {
+  if constexpr (EPL >= 2 && (EPL & 1) == 0) {
+    if (n <= 16 * EPL) {   // warp-uniform
+      const unsigned lt = (1u << lane) - 1u;
+      int base = 0;
+      __syncwarp();
+#pragma unroll
+      for (int m = 0; m < EPL; ++m) {
+        const bool keep = v[m] != ~0ull;
+        const unsigned mask = __ballot_sync(0xffffffffu, keep);
+        if (keep) buf[base + __popc(mask & lt)] = v[m];
+        base += __popc(mask);
+      }
+      __syncwarp();
+      u64 w[EPL / 2];
+#pragma unroll
+      for (int m = 0; m < EPL / 2; ++m) w[m] = (m * 32 + lane < n) ? buf[m * 32 + lane] : ~0ull;
+      sort_and_write_run<EPL / 2>(w, n, lane, buf, dst, J);
+      return;
+    }
+  }
+  warp_sort<EPL>(v, lane);
+#pragma unroll
+  for (int m = 0; m < EPL; ++m) {
+    const int rank = lane * EPL + m;
+    if (rank < n)
+      dst[rank] = make_uint2(__float_as_uint(sortable_to_float((uint32_t)(v[m] >> 32))), (uint32_t)v[m] * (uint32_t)J);
+  }
+}
+
 // One warp per input pixel p = (b*H + h)*W + w: runs[p*stride ..] receives the pixel's inputs that can spike
 // as (float bits, c*J) in ascending order followed by a terminator; counts[p] their number.
 template <int EPL>
 __global__ void __launch_bounds__(kPixelWarps * 32)
 snn_pixel_runs_kernel(const float* __restrict__ x, int npix, int C, int J, float maxcomp,
                       WalkEntry* __restrict__ runs, int* __restrict__ counts, int stride) {
+  __shared__ u64 compact[kPixelWarps][EPL >= 2 ? 16 * EPL : 1];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   for (int p = blockIdx.x * kPixelWarps + warp; p < npix; p += gridDim.x * kPixelWarps) {
@@ -89,15 +172,8 @@ snn_pixel_runs_kernel(const float* __restrict__ x, int npix, int C, int J, float
       v[m] = keep ? (((u64)float_to_sortable(val) << 32) | (unsigned)c) : ~0ull;
       n += __popc(__ballot_sync(0xffffffffu, keep));
     }
-    warp_bitonic_sort<EPL>(v, lane);
     WalkEntry* dst = runs + (size_t)p * stride;
-#pragma unroll
-    for (int m = 0; m < EPL; ++m) {
-      const int rank = lane * EPL + m;
-      if (rank < n)
-        dst[rank] = make_uint2(__float_as_uint(sortable_to_float((uint32_t)(v[m] >> 32))),
-                               (uint32_t)v[m] * (uint32_t)J);
-    }
+    sort_and_write_run<EPL>(v, n, lane, compact[warp], dst, J);
     if (lane == 0) {
       dst[n] = make_uint2(kRunEndBits, 0u);
       counts[p] = n;
@@ -165,7 +241,7 @@ snn_small_rows_kernel(const Geometry g, const float* __restrict__ x, WalkEntry* 
       v[m] = keep ? (((u64)float_to_sortable(val) << 32) | (unsigned)i) : ~0ull;
       n += __popc(__ballot_sync(0xffffffffu, keep));
     }
-    warp_bitonic_sort<EPL>(v, lane);
+    warp_sort<EPL>(v, lane);
     WalkEntry* dst = lists + (size_t)r * istride;
 #pragma unroll
     for (int m = 0; m < EPL; ++m) {
@@ -408,10 +484,16 @@ int launch_small_rows(const Geometry& g, const float* x, WalkEntry* lists, int* 
   const long cap = (long)li.num_sms * 8;
   if (grid > cap) grid = cap;
   const int epl = (g.I + 31) / 32;
-  if (epl <= 1) snn_small_rows_kernel<1><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
-  else if (epl <= 2) snn_small_rows_kernel<2><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
-  else if (epl <= 4) snn_small_rows_kernel<4><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
-  else snn_small_rows_kernel<8><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride);
+  switch (epl) {   // 3, 5, 6, 7 keys per lane: the block network (a bitonic one would round them up to 4 and 8)
+    case 1: snn_small_rows_kernel<1><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 2: snn_small_rows_kernel<2><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 3: snn_small_rows_kernel<3><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 4: snn_small_rows_kernel<4><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 5: snn_small_rows_kernel<5><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 6: snn_small_rows_kernel<6><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    case 7: snn_small_rows_kernel<7><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+    default: snn_small_rows_kernel<8><<<(int)grid, kPixelWarps * 32, 0, s>>>(g, x, lists, nvalid, istride); break;
+  }
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }

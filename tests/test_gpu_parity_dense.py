@@ -164,7 +164,7 @@ def test_dense_repeatable():
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
 
 
-@pytest.mark.parametrize("I", [1, 31, 32, 33, 64, 100, 147, 255, 256])
+@pytest.mark.parametrize("I", [1, 31, 32, 33, 64, 70, 100, 147, 170, 200, 255, 256])
 def test_dense_short_rows_by_the_register_network_match_the_row_sort(I):
     """Rows of at most 256 inputs are sorted by a network in registers; the per-row radix sort forced through the
     measurement build gives the same lists (equal inputs in index order), hence the same bits. Inputs include
