@@ -44,6 +44,9 @@ CONV_CASES = [
     (97, 4, 4, 4, 32, 3, 3, 1, 1, 64, 1.0, "SAME", "ref"),
     (98, 2, 16, 16, 16, 2, 2, 1, 1, 40, 1.0, "SAME", "cfg"),
     (99, 3, 16, 2, 64, 3, 1, 1, 1, 32, 0.0, "SAME", "ref"),      # a map 2 wide, a 3x1 kernel, no bias
+    (100, 1, 5, 5, 4, 7, 7, 1, 1, 8, 1.0, "SAME", "test"),       # 4 channels under a 7x7 window: 49 taps, one per lane
+    (101, 2, 1, 1, 16, 1, 1, 1, 1, 4, 1.0, "SAME", "test"),      # a 1x1 map, a 1x1 kernel: one field per stage
+    (102, 1, 3, 40, 32, 3, 3, 1, 1, 36, 1.0, "SAME", "ref"),     # a map 40 wide: blocks of 16, 16 and 8 columns
 ]
 
 
@@ -107,7 +110,7 @@ def test_conv_backward(case):
 
 
 # ---- kernel variants against each other (measurement build: the kernel choice of a call is given explicitly)
-VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 51, 82, 84, 86, 92, 93, 94, 96, 97, 98, 99)]
+VARIANT_CASES = [c for c in CONV_CASES if c[0] in (44, 48, 51, 82, 84, 86, 92, 93, 94, 96, 97, 98, 99, 100, 101, 102)]
 
 
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
