@@ -37,14 +37,16 @@ constexpr int kTileI = 128;     // dW output tile: 128 fan-in rows x 64 outputs,
 template <bool V4>   // V4: n and nx are multiples of 4 and all pointers 16-byte aligned: 16-byte loads and stores
 __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __restrict__ out, float* __restrict__ u,
                              size_t n, float maxcomp, const float* __restrict__ xin, size_t nx, float maxv,
-                             int* __restrict__ exact_flag) {
+                             int* __restrict__ exact_flag, unsigned* __restrict__ nz_count) {
   const float tiny = 8.67361737988e-19f;   // 2^-60
   const float big = 1.26765060023e30f;     // 2^100
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const size_t t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   bool odd = false;
+  unsigned nz = 0;           // outputs of this thread that carry a gradient (u != 0)
   auto one = [&](float y, float g, float inv) {
     const float uu = (y > maxcomp) ? 0.f : g * inv;
+    nz += uu != 0.f;
     const float ya = fabsf(y);
     odd |= (ya > 0.f && ya < tiny) || !(fabsf(uu) < big);
     return uu;
@@ -72,6 +74,11 @@ __global__ void snn_u_kernel(const float* __restrict__ grad, const float* __rest
     for (size_t e = t0; e < nx; e += stride) scan(__ldg(xin + e));
   }
   if (odd) *exact_flag = 1;
+  if (nz_count != nullptr) {   // one atomic per warp: *nz_count = number of outputs with a gradient (zero before the launch)
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) nz += __shfl_xor_sync(0xffffffffu, nz, d);
+    if ((threadIdx.x & 31) == 0 && nz != 0u) atomicAdd(nz_count, nz);
+  }
 }
 
 // acc += [x <= y] * u * w as one compare and one predicated FMA
@@ -102,8 +109,9 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // the arithmetic of tile t and parked in registers, shared memory is double buffered.
 template <bool VEC>   // VEC: J % 4 == 0, tiles are fetched with 16-byte loads
 __global__ void __launch_bounds__(kBwdThreads)
-snn_dx_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
+snn_dx_kernel(const DxGate gate, const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
               const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
+  if (gate.nz != nullptr && __ldg(gate.nz) <= gate.threshold) return;   // the list-walking kernel takes this call
   __shared__ __align__(16) float Ys[2][kTile * kJTP];
   __shared__ __align__(16) float Us[2][kTile * kJTP];
   __shared__ __align__(16) float Ws[2][kTile * kJTP];
@@ -283,8 +291,9 @@ constexpr int kYStride = kWideP + 4;
 constexpr int kWStride = kTile + 4;
 
 __global__ void __launch_bounds__(kBwdThreads)
-snn_dx_wide_kernel(const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
+snn_dx_wide_kernel(const DxGate gate, const Geometry g, const float* __restrict__ uv, const float* __restrict__ x,
                    const float* __restrict__ w, const float* __restrict__ out, float* __restrict__ dx) {
+  if (gate.nz != nullptr && __ldg(gate.nz) <= gate.threshold) return;   // the list-walking kernel takes this call
   __shared__ __align__(16) float Ys[2][kJT * kYStride];
   __shared__ __align__(16) float Us[2][kJT * kYStride];
   __shared__ __align__(16) float Ws[2][kJT * kWStride];
@@ -900,6 +909,7 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
   if (!ws || ws_bytes < lay.total) return E_WORKSPACE;
   float* uv = static_cast<float*>(ws);
   int* exact_flag = reinterpret_cast<int*>(static_cast<unsigned char*>(ws) + lay.flag);
+  unsigned* nz_count = reinterpret_cast<unsigned*>(exact_flag + 1);   // outputs with a gradient, counted by snn_u_kernel
   float* planes = reinterpret_cast<float*>(static_cast<unsigned char*>(ws) + lay.planes);
   void* dx_scratch = static_cast<unsigned char*>(ws) + lay.dx_scratch;
   // 16-byte tile loads need J % 4 == 0 and 16-byte aligned bases (rows then start aligned too)
@@ -909,12 +919,12 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const size_t n = (size_t)g.R * g.J;
     size_t blocks = (n + 255) / 256;
     if (blocks > (size_t)li.num_sms * 8) blocks = (size_t)li.num_sms * 8;
-    if (cudaMemsetAsync(exact_flag, 0, sizeof(int), s) != cudaSuccess) return E_CUDA;
+    if (cudaMemsetAsync(exact_flag, 0, 2 * sizeof(int), s) != cudaSuccess) return E_CUDA;   // the flag and the counter behind it
     const size_t nx = g.is_conv ? (size_t)g.B * g.H * g.W * g.C : (size_t)g.R * g.I;
     const bool v4 = (n % 4 == 0) && (nx % 4 == 0) &&
                     (((uintptr_t)grad | (uintptr_t)out | (uintptr_t)uv | (uintptr_t)x) & 15) == 0;
-    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
-    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag);
+    if (v4) snn_u_kernel<true><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, nz_count);
+    else snn_u_kernel<false><<<(int)blocks, 256, 0, s>>>(grad, out, uv, n, g.maxv - 0.1f, x, nx, g.maxv, exact_flag, nz_count);
     count_launch();
     if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   }
@@ -930,18 +940,29 @@ int launch_backward(const Geometry& g, const float* grad, const float* x, const 
     const int CH = g.is_conv ? g.C : g.I;
     const long P = g.is_conv ? (long)g.B * g.H * g.W : g.R;
     dim3 grid((unsigned)((P + kTile - 1) / kTile), (CH + kTile - 1) / kTile);
-    if (want_dx_sparse(g, opt) && dx_sparse_supported(g, x, dx)) {
-      rc = launch_dx_sparse(g, uv, x, w, out, dx, dx_scratch, li, sdx);
-    } else if (vec && P >= 64 * kWideP && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {   // it stores dx 16 bytes at a time
-      dim3 gridw((unsigned)((P + kWideP - 1) / kWideP), (CH + kTile - 1) / kTile);
-      snn_dx_wide_kernel<<<gridw, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
-    } else if (vec) {
-      snn_dx_kernel<true><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
-    } else {
-      snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(g, uv, x, w, out, dx);
+    // Conv layers the list-walking kernel supports: with dx_kernel 0 both kernels are queued and the device picks
+    // (DxGate: the list-walking one up to 40 % of the outputs carrying a gradient -- its time grows with that share,
+    // the dense tile's does not; they cross near 41 % on the benchmark layers); 1 / 2 name one.
+    const bool sparse_ok = want_dx_sparse(g, opt) && dx_sparse_supported(g, x, dx);
+    const bool both = sparse_ok && opt.dx_kernel == 0;
+    DxGate gate = {nullptr, 0u};
+    if (both) {
+      gate.nz = nz_count;
+      gate.threshold = (unsigned)(((size_t)g.R * g.J) / 5 * 2);
     }
-    count_launch();
-    if (rc == OK && cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+    if (sparse_ok) rc = launch_dx_sparse(g, uv, x, w, out, dx, dx_scratch, gate, li, sdx);
+    if (rc == OK && (!sparse_ok || both)) {
+      if (vec && P >= 64 * kWideP && (reinterpret_cast<uintptr_t>(dx) & 15) == 0) {   // it stores dx 16 bytes at a time
+        dim3 gridw((unsigned)((P + kWideP - 1) / kWideP), (CH + kTile - 1) / kTile);
+        snn_dx_wide_kernel<<<gridw, kBwdThreads, 0, sdx>>>(gate, g, uv, x, w, out, dx);
+      } else if (vec) {
+        snn_dx_kernel<true><<<grid, kBwdThreads, 0, sdx>>>(gate, g, uv, x, w, out, dx);
+      } else {
+        snn_dx_kernel<false><<<grid, kBwdThreads, 0, sdx>>>(gate, g, uv, x, w, out, dx);
+      }
+      count_launch();
+      if (cudaGetLastError() != cudaSuccess) rc = E_CUDA;
+    }
   }
   if (rc == OK && (parts & 2)) {
     const float scale = dw_scale(g);

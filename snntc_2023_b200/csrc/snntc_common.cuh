@@ -50,7 +50,8 @@ struct Options {
   int backward_parts = 3;   // bit 0: dX, bit 1: dW
   int dw_kernel = 0;        // 0 auto, 1 dense register tile, 2 row-skipping kernel (conv, C % 4 == 0) with per-thread
                             // copies, 4 the row-skipping kernel fed through tensor maps (where the shape allows)
-  int dx_kernel = 0;        // 0 auto, 1 dense register tile, 2 list-walking kernel (conv, C % 4 == 0, C <= 512)
+  int dx_kernel = 0;        // 0 auto (conv layers the list-walking kernel supports: both queued, the device picks by
+                            // the share of outputs with a gradient), 1 dense register tile, 2 list-walking kernel
   int overlap = -1;         // -1 library setting (snntc_set_overlap), 0 one stream, 1 dX beside dW
 };
 
@@ -129,13 +130,22 @@ int launch_dw_tma(const Geometry& g, const float* uv, const float* x, const floa
 // CTAs of that kernel that gave up waiting for their copies (current device, since the library was loaded)
 unsigned long long dw_copy_timeouts();
 
+// Which dX kernel of a conv layer is faster depends on how many outputs carry a gradient, which only the device knows
+// (snn_u_kernel counts them into *nz): the library queues BOTH, and each looks at the count first -- the list-walking
+// kernels return at once when more than `threshold` outputs carry one, the dense register-tile kernel when at most
+// that many do. nz == nullptr: no gate, the kernel runs. Both kernels give the same bits.
+struct DxGate {
+  const unsigned* nz;
+  unsigned threshold;
+};
+
 // dX by a kernel that walks, per input pixel, the lists of outputs with a non-zero gradient factor
 // (snntc_dx_sparse.cu). dx_sparse_bytes is its scratch (lists, their lengths, transposed weights).
 bool dx_sparse_shape_ok(const Geometry& g);
 bool dx_sparse_supported(const Geometry& g, const float* x, const float* dx);
 size_t dx_sparse_bytes(const Geometry& g);
 int launch_dx_sparse(const Geometry& g, const float* uv, const float* x, const float* w, const float* out, float* dx,
-                     void* scratch, const LaunchInfo& li, cudaStream_t s);
+                     void* scratch, DxGate gate, const LaunchInfo& li, cudaStream_t s);
 
 // monotone map float bits -> unsigned so that an unsigned compare orders like the float compare
 __host__ __device__ __forceinline__ uint32_t float_to_sortable(float f) {

@@ -31,7 +31,8 @@ constexpr int kThreads = 256;
 // ascending j; count[r] their number.
 __global__ void __launch_bounds__(kThreads)
 snn_act_lists_kernel(const float* __restrict__ out, const float* __restrict__ uv, int R, int J,
-                     uint4* __restrict__ list, int* __restrict__ count) {
+                     uint4* __restrict__ list, int* __restrict__ count, const DxGate gate) {
+  if (gate.nz != nullptr && __ldg(gate.nz) > gate.threshold) return;   // the dense kernel takes this call
   const int lane = threadIdx.x & 31;
   const int warps = (gridDim.x * blockDim.x) >> 5;
   for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < R; r += warps) {
@@ -53,7 +54,9 @@ snn_act_lists_kernel(const float* __restrict__ out, const float* __restrict__ uv
 }
 
 // Wt[(tap*J + j)*C + c] = W[(tap*C + c)*J + j]  (the bias row is not part of dX)
-__global__ void snn_weight_transpose_kernel(const float* __restrict__ w, float* __restrict__ wt, int taps, int C, int J) {
+__global__ void snn_weight_transpose_kernel(const float* __restrict__ w, float* __restrict__ wt, int taps, int C, int J,
+                                            const DxGate gate) {
+  if (gate.nz != nullptr && __ldg(gate.nz) > gate.threshold) return;
   const size_t n = (size_t)taps * C * J;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += stride) {
@@ -84,7 +87,9 @@ constexpr int kStage = 256;   // staged list entries per warp and round
 template <int CPL, int LPP>
 __global__ void __launch_bounds__(kThreads)
 snn_dx_sparse_kernel(const Geometry g, const float* __restrict__ x, const float* __restrict__ wt,
-                     const uint4* __restrict__ list, const int* __restrict__ count, float* __restrict__ dx) {
+                     const uint4* __restrict__ list, const int* __restrict__ count, float* __restrict__ dx,
+                     const DxGate gate) {
+  if (gate.nz != nullptr && __ldg(gate.nz) > gate.threshold) return;
   constexpr int PPW = 32 / LPP;                       // pixels per warp
   constexpr int SB = kStage / PPW;                    // staged entries per pixel and round
   constexpr int UN = CPL <= 4 ? 4 : 2;                // entries whose weight reads are in flight together
@@ -205,13 +210,13 @@ size_t align256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 template <int CPL, int LPP>
 int launch_one(const Geometry& g, const float* x, const float* wt, const uint4* list, const int* count, float* dx,
-               const LaunchInfo& li, cudaStream_t s) {
+               DxGate gate, const LaunchInfo& li, cudaStream_t s) {
   const long P = (long)g.B * g.H * g.W;
   const long warps = (P + (32 / LPP) - 1) / (32 / LPP);
   long grid = (warps + (kThreads / 32) - 1) / (kThreads / 32);
   const long cap = (long)li.num_sms * 16;
   if (grid > cap) grid = cap;
-  snn_dx_sparse_kernel<CPL, LPP><<<(int)grid, kThreads, 0, s>>>(g, x, wt, list, count, dx);
+  snn_dx_sparse_kernel<CPL, LPP><<<(int)grid, kThreads, 0, s>>>(g, x, wt, list, count, dx, gate);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? OK : E_CUDA;
 }
@@ -235,7 +240,7 @@ size_t dx_sparse_bytes(const Geometry& g) {
 }
 
 int launch_dx_sparse(const Geometry& g, const float* uv, const float* x, const float* w, const float* out, float* dx,
-                     void* scratch, const LaunchInfo& li, cudaStream_t s) {
+                     void* scratch, DxGate gate, const LaunchInfo& li, cudaStream_t s) {
   unsigned char* base = static_cast<unsigned char*>(scratch);
   uint4* list = reinterpret_cast<uint4*>(base);
   int* count = reinterpret_cast<int*>(base + align256((size_t)g.R * g.J * sizeof(uint4)));
@@ -243,23 +248,23 @@ int launch_dx_sparse(const Geometry& g, const float* uv, const float* x, const f
 
   long grid = ((long)g.R + (kThreads / 32) - 1) / (kThreads / 32);
   if (grid > (long)li.num_sms * 16) grid = (long)li.num_sms * 16;
-  snn_act_lists_kernel<<<(int)grid, kThreads, 0, s>>>(out, uv, g.R, g.J, list, count);
+  snn_act_lists_kernel<<<(int)grid, kThreads, 0, s>>>(out, uv, g.R, g.J, list, count, gate);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
   const size_t nw = (size_t)g.Kh * g.Kw * g.C * g.J;
   long tg = (long)((nw + 255) / 256);
   if (tg > (long)li.num_sms * 8) tg = (long)li.num_sms * 8;
-  snn_weight_transpose_kernel<<<(int)tg, 256, 0, s>>>(w, wt, g.Kh * g.Kw, g.C, g.J);
+  snn_weight_transpose_kernel<<<(int)tg, 256, 0, s>>>(w, wt, g.Kh * g.Kw, g.C, g.J, gate);
   count_launch();
   if (cudaGetLastError() != cudaSuccess) return E_CUDA;
 
   const int C = g.C;
-  if (C <= 16) return launch_one<4, 4>(g, x, wt, list, count, dx, li, s);
-  if (C <= 32) return launch_one<4, 8>(g, x, wt, list, count, dx, li, s);
-  if (C <= 64) return launch_one<4, 16>(g, x, wt, list, count, dx, li, s);
-  if (C <= 128) return launch_one<4, 32>(g, x, wt, list, count, dx, li, s);
-  if (C <= 256) return launch_one<8, 32>(g, x, wt, list, count, dx, li, s);
-  return launch_one<16, 32>(g, x, wt, list, count, dx, li, s);
+  if (C <= 16) return launch_one<4, 4>(g, x, wt, list, count, dx, gate, li, s);
+  if (C <= 32) return launch_one<4, 8>(g, x, wt, list, count, dx, gate, li, s);
+  if (C <= 64) return launch_one<4, 16>(g, x, wt, list, count, dx, gate, li, s);
+  if (C <= 128) return launch_one<4, 32>(g, x, wt, list, count, dx, gate, li, s);
+  if (C <= 256) return launch_one<8, 32>(g, x, wt, list, count, dx, gate, li, s);
+  return launch_one<16, 32>(g, x, wt, list, count, dx, gate, li, s);
 }
 
 }  // namespace snntc

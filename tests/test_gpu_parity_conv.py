@@ -209,6 +209,11 @@ def test_conv_dx_kernels_agree(case):
         P.check_close(dx2.cpu().numpy(), ref["dx"], "list-walking dX %s" % (case,), abs_sum=ref["dx_abs"])
         P.check_close(dw2.cpu().numpy(), ref["dw"], "dW beside the list-walking dX %s" % (case,), abs_sum=ref["dw_abs"])
         assert torch.equal(dx1, dx2), "dense and list-walking dX differ in bits"
+        # the library's own choice queues both and lets the device pick by the share of outputs with a gradient (the
+        # dense one at no zeros, the list-walking one at 80 % zeros): the same bits either way, and dx fully written
+        dx0, _, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options())
+        assert torch.equal(dx0, dx1)
+        assert torch.equal(ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl)[0], dx1)   # product library
     # the pre-padded calling convention: padding pixels hold MAX and get a zero gradient
     xp = torch.from_numpy(O.pad_like_reference(x, Kh, Kw, Sh, Sw, padding)).cuda()
     a, _, _ = ops.snn_cv_grad(gd, xp, wd, params, out, opts=_lib.options(dx_kernel=1))
