@@ -248,3 +248,22 @@ extern "C" void merge3(const uint2* a, const uint2* b, const uint2* c, unsigned 
                 assert int(sizes.sum()) == total and sizes.min() >= 0
                 assert np.array_equal(dst2[:total], dst[:total])
                 assert np.all(dst2[total:, 0] == 0xDEADBEEF)
+
+
+def test_bench_reference_arm_prints_exactly_one_json_line():
+    """The CPU arm of the benchmark (the reference's operators on the host cores) on a two-sample step: standard output
+    holds one line, a JSON object with the keys the contract names; everything else goes to standard error."""
+    import json
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                        "--warmup", "0", "--cpu-sample", "2"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [l for l in r.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1, r.stdout[:500]
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["steps"] == 1
+    assert line["metric"] == "snn_tc_fwd_bwd_samples_per_s" and line["unit"] == "samples/s" and line["higher_is_better"] is True
+    assert line["value"] > 0 and line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["value"] == line["value"] and line["e2e"]["h2d_bytes_per_step"] == 0
+    assert line["gpu_launches"] == 0 and line["config"]["workload"] == "cifar"
