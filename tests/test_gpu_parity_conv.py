@@ -187,6 +187,9 @@ def test_conv_dw_kernels_agree(case):
     ref = O.cv_backward(g, x, w, params, outc[:B], outc[B:], "f64")
     with np.errstate(over="ignore", invalid="ignore"):
         P.check_close(dw4.cpu().numpy(), ref["dw"], "row-skipping dW, unscaled loop %s" % (case,), abs_sum=ref["dw_abs"])
+        # the tensor-map kernel's unscaled loop: its out-of-image inputs are NaN and must still count as "never spikes"
+        _, dw7, _ = ops.snn_cv_grad(gd, xd, wd, params, out, pt, pl, opts=_lib.options(dw_kernel=4))
+        P.check_close(dw7.cpu().numpy(), ref["dw"], "tensor-map dW, unscaled loop %s" % (case,), abs_sum=ref["dw_abs"])
 
 
 @pytest.mark.parametrize("case", VARIANT_CASES, ids=_ids)
