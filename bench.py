@@ -10,7 +10,8 @@ input; for the single-layer configs it is the layer's forward plus backward on a
 gradient. Rank 0 prints ONE JSON line: the headline workload (--config, default the CIFAR-shaped
 network) with its roofline, CPU baseline and reference-GPU leg, then short runs of the other
 configurations under "configs", a small parity check against the CPU oracle under "parity", and at
-N>1 the data-parallel gradient check "dp_parity_rel_l2" and an ImageNet-shaped step.
+N>1 the data-parallel checks "dp_parity_rel_l2" (gradient) and "dp_param_max_abs_spread" (weights equal on all ranks
+after the timed steps) and an ImageNet-shaped step.
 """
 import argparse
 import json
@@ -266,27 +267,63 @@ class NetWorkload:
         return (pinned[0].to(self.device, non_blocking=True), pinned[1].to(self.device, non_blocking=True))
 
     def enable_graph(self, example_batch):
-        """Capture the whole step once; later steps replay it (snntc_2023_b200.graph.GraphedStep)."""
+        """Capture the step once; later steps replay it (snntc_2023_b200.graph.GraphedStep). One process: the whole
+        step is one graph. Several: the collective stays an ordinary NCCL call between two graphs -- everything up to
+        the gradient (encoding, forward, loss, backward) and the optimiser update -- so that no rank ever captures a
+        collective."""
         from snntc_2023_b200.graph import GraphedStep
-        self.graphed = GraphedStep(lambda t, lab: self.eager_step((t, lab)), list(example_batch))
+        if self.world == 1:
+            self.graphed = GraphedStep(lambda t, lab: self.eager_step((t, lab)), list(example_batch))
+        else:
+            self.graphed = SplitGraphedStep(self, list(example_batch))
 
     def step(self, dev_batch):
         if self.graphed is not None and self.optimize and (self.collective or self.world == 1):
             return self.graphed(*dev_batch)
         return self.eager_step(dev_batch)
 
-    def eager_step(self, dev_batch):
+    def forward_backward(self, dev_batch):
         t, lab = dev_batch
         z = self.train.encode(t, one_minus=False)
         loss = self.net.loss(z, lab)
         # the reference's train_step adds the constraint cost to the loss (snntc-mnist.py:76-80)
         self.net.backward(loss + self.net.constraint_cost(CONSTRAINT_K, CONSTRAINT_K2))
+        return loss.detach()
+
+    def eager_step(self, dev_batch):
+        loss = self.forward_backward(dev_batch)
         if self.world > 1 and self.collective:
             from snntc_2023_b200 import ddp
             ddp.allreduce_mean_(self.net.flat_grad, self.world)
         if self.optimize:
             self.opt.step()
-        return loss.detach()
+        return loss
+
+
+class SplitGraphedStep:
+    """A data-parallel step as two CUDA graphs around one eager all-reduce of the flat gradient bucket."""
+
+    def __init__(self, wl, example_batch):
+        from snntc_2023_b200.graph import GraphedStep
+        self.wl = wl
+        self.fwd_bwd = GraphedStep(lambda t, lab: wl.forward_backward((t, lab)), example_batch)
+
+        def update():
+            wl.opt.step()
+            return wl.net.flat_param[:1]
+        # (no warm-up runs: they would apply this rank's own, not yet reduced, gradient to its copy of the weights)
+        self.update = GraphedStep(update, [], warmup=0)
+        self.replays = 0
+        self.library_launches_per_replay = (self.fwd_bwd.library_launches_per_replay +
+                                            self.update.library_launches_per_replay)
+
+    def __call__(self, *inputs):
+        from snntc_2023_b200 import ddp
+        loss = self.fwd_bwd(*inputs)
+        ddp.allreduce_mean_(self.wl.net.flat_grad, self.wl.world)
+        self.update()
+        self.replays += 1
+        return loss
 
 
 class LayerWorkload:
@@ -580,13 +617,14 @@ def build_workload(config, batch, device, world, use_graph):
         wl.step(resident[i % nb])
     torch.cuda.synchronize()
     note = "eager launches"
-    if use_graph and world == 1:   # multi-GPU steps keep eager launches (collective inside)
+    if use_graph and (world == 1 or kind == "net"):
         try:
             wl.enable_graph(resident[0])
             for i in range(3):
                 wl.step(resident[i % nb])
             torch.cuda.synchronize()
-            note = "whole step replayed as one CUDA graph"
+            note = "whole step replayed as one CUDA graph" if world == 1 else \
+                "forward+backward and optimiser update replayed as two CUDA graphs around one eager NCCL all-reduce"
         except Exception as e:   # capture is an optimisation: fall back to eager launches and say so
             wl.graphed = None
             note = "eager launches (graph capture failed: %s)" % (str(e).splitlines()[0][:120],)
@@ -647,8 +685,15 @@ def run_gpu_arm(args):
 
     # ---- N > 1: what the all-reduce computed against the gradient of the global batch formed on rank 0 alone
     dp_parity = None
+    param_spread = None
     if world > 1 and kind == "net":
         from snntc_2023_b200 import ddp
+        # after the timed steps every rank must hold the same weights: largest |w - w of rank 0| over all ranks
+        ref_param = wl.net.flat_param.detach().clone()
+        dist.broadcast(ref_param, src=0)
+        spread = (wl.net.flat_param.detach() - ref_param).abs().max().reshape(1)
+        dist.all_reduce(spread, op=dist.ReduceOp.MAX)
+        param_spread = float(spread.item())
         opt = wl.optimize
         wl.optimize = False
         wl.eager_step(resident[0])                  # every rank: its own first batch, gradients all-reduced to the mean
@@ -759,6 +804,7 @@ def run_gpu_arm(args):
         }
         if dp_parity is not None:
             line["dp_parity_rel_l2"] = dp_parity
+            line["dp_param_max_abs_spread"] = param_spread
 
     # ---- the other configurations, briefly (the headline's objects are released first)
     extras = {}
