@@ -667,8 +667,6 @@ def run_gpu_arm(args):
     device = torch.device("cuda", local)
     if world > 1:
         import datetime
-        # whatever NCCL logs (its version line, NCCL_DEBUG output) goes to stderr: stdout carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         # a short timeout: a rank that misses a collective must end the run in minutes, not hang it
         dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=120))
     lib = _lib.load()
